@@ -1,0 +1,161 @@
+/* C ABI of libofa_b200.so: a B200-native persistent megakernel that trains a GPT and serves it from the live weights.
+ *
+ * The reference program (Bobliuuu/open-flapping-airplanes, llm/b200/megakernel/ofa.cu) has no library boundary: its
+ * main() builds the phase tables, uploads them and performs the one launch. This header exports exactly what that
+ * main() does, split into calls a host program (C++, or Python through ctypes) can drive. Every entry point cites the
+ * part of the reference it replaces. Plain pointers and sizes only; the caller owns host buffers, the library owns
+ * device memory. No call blocks forever and no call exits the process: errors come back as ofa_status codes and
+ * ofa_last_error() gives the text.
+ *
+ * Two levels:
+ *   model level  - ofa_create / ofa_load_weights / ofa_set_tokens / ofa_launch / ofa_wait / ofa_read_*  (ofa.cu:394-766)
+ *   task level   - ofa_run_phases: run an explicit list of phase descriptors through the same persistent scheduler; this
+ *                  is the reference's task API (PhaseDesc/Job, ofa.cu:87-117) and what its per-library tests drive
+ *                  (llm/gemm/test_gemm.cu:20-49, llm/attention/test_attention.cu:45-77, llm/elementwise/test_elementwise.cu:19-47).
+ */
+#ifndef OFA_B200_H
+#define OFA_B200_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct ofa_ctx ofa_ctx;
+
+typedef enum {
+  OFA_OK = 0,
+  OFA_TIMEOUT = 1,        /* ofa_wait: the launch is still running after timeout_ms                       */
+  OFA_DEVICE_ABORT = 2,   /* a bounded device-side wait expired; see ofa_status_t.{code,phase,task,block}  */
+  OFA_CUDA_ERROR = 3,
+  OFA_BAD_CONFIG = 4,
+  OFA_BAD_ARGUMENT = 5,
+  OFA_NOT_LAUNCHED = 6
+} ofa_code;
+
+typedef struct {
+  int code;               /* ofa_code */
+  int dev_code;           /* device status: 1 dependency timeout, 2/3/4 mbarrier timeouts, 5 smem misaligned, 6 external flag timeout, 7 bad descriptor */
+  int phase, task, block, aux;
+} ofa_status_t;
+
+enum { OFA_DTYPE_BF16 = 0, OFA_DTYPE_F32 = 1 };
+enum { OFA_MODE_TRAIN = 0, OFA_MODE_FORWARD = 1, OFA_MODE_NO_OPT = 2 };
+
+/* Replaces the compile-time constants and argv/env flags of the reference (ofa.cu:61-84, 395-430, 696). */
+typedef struct {
+  int vocab, d_model, n_layer, n_head, ctx_len, batch;   /* ffn = 4*d_model, head_dim = d_model/n_head           */
+  int valid_vocab;          /* ids >= valid_vocab are never sampled (ofa.cu:71 VALID)                             */
+  int tied_head;            /* 1: LM head = wte (reference), 0: separate lm_head[V,D] after wpe in the flat layout */
+  int dtype;                /* OFA_DTYPE_BF16: d_model 768 / head_dim 64, tensor cores; OFA_DTYPE_F32: d_model 64 / head_dim 16 */
+  int mode;                 /* OFA_MODE_*: full training step, forward through logits only, or forward+backward without AdamW (ofa.cu --no-opt) */
+  int sched_steps, warmup, constant_lr;
+  float lr_max, lr_min, beta1, beta2, eps, weight_decay;
+  unsigned long long data_seed;   /* window starts when no starts table is set (ofa.cu:160) */
+  int infer_sms, reserved_sms, train_sms;   /* SM split (ofa.cu:384-391); train_sms <= 0: all remaining SMs       */
+  int use_decode;           /* run the serving job concurrently                                                   */
+  int n_prompt; int prompt[32]; int answer_len; float temperature; unsigned long long decode_seed;
+  int decode_out_cap;       /* size of the pinned token ring                                                      */
+  int dp_world;             /* gradient scale 1/dp_world is folded into AdamW                                      */
+  int grad_bf16;            /* weight gradients are written as bf16 (the all-reduce bucket format)                */
+  int ext_sync;             /* 1: gradients are cut into buckets; the graph raises a "ready" flag per bucket and holds the bucket's AdamW until the matching "done" flag is raised from outside (the all-reduce) */
+  int bucket_bytes;         /* target bucket size for ext_sync (0 = 25 MiB)                                       */
+  int gemm_nsub;            /* consecutive 128-wide N tiles per GEMM task (0 = default)                           */
+  double timeout_s;         /* device-side bound for any dependency wait (0 = default 20 s)                       */
+  int device;               /* CUDA device ordinal                                                                 */
+} ofa_config;
+
+/* preset: "tiny" (BASELINE config 1) or "gpt_s" (config 2). */
+int ofa_default_config(ofa_config* cfg, const char* preset);
+
+/* lifecycle: replaces the body of main() up to the launch (ofa.cu:415-707). One ctx per device. */
+int ofa_create(const ofa_config* cfg, ofa_ctx** out);
+void ofa_destroy(ofa_ctx* ctx);
+const char* ofa_last_error(const ofa_ctx* ctx);   /* ctx may be NULL: error of the last failed ofa_create on this thread */
+
+/* flat parameter layout (ofa.cu:338-350 `struct Layout`): wte, wpe, [lm_head], per layer {g1, Wqkv, Wo, g2, Wup, Wdn}, gf */
+size_t ofa_num_params(const ofa_ctx* ctx);
+/* name: "wte","wpe","lm_head","gf","L<l>.g1|Wqkv|Wo|g2|Wup|Wdn". Returns 0 and fills offset/count (elements), or OFA_BAD_ARGUMENT. */
+int ofa_param_span(const ofa_ctx* ctx, const char* name, size_t* offset, size_t* count);
+
+/* weights in/out: replaces --init / --dump-w / --dump-grads (ofa.cu:491, 762-763). fp32, flat layout order. */
+int ofa_load_weights(ofa_ctx* ctx, const float* flat, size_t n);
+int ofa_read_weights(ofa_ctx* ctx, float* out, size_t n);
+int ofa_read_grads(ofa_ctx* ctx, float* out, size_t n);     /* converted to fp32 when grad_bf16 */
+int ofa_read_adam_m(ofa_ctx* ctx, float* out, size_t n);
+int ofa_read_adam_v(ofa_ctx* ctx, float* out, size_t n);
+int ofa_load_adam_state(ofa_ctx* ctx, const float* m, const float* v, size_t n, int step_base);   /* resume */
+
+/* tokens: replaces --data / --starts (ofa.cu:513-528). starts is [nsteps][batch] window offsets, or NULL for hashed starts. */
+int ofa_set_tokens(ofa_ctx* ctx, const uint32_t* tokens, size_t n);
+int ofa_set_starts(ofa_ctx* ctx, const uint32_t* starts, size_t nsteps);
+
+/* run: replaces the launch + event polling loop (ofa.cu:710-716). ofa_launch is asynchronous and runs `nsteps` more
+ * training steps (or, without a training job, `nsteps` decode tokens) in ONE persistent launch; ofa_wait returns
+ * OFA_TIMEOUT if it is still running after timeout_ms, OFA_DEVICE_ABORT if a bounded device wait expired. */
+int ofa_launch(ofa_ctx* ctx, int nsteps);
+int ofa_wait(ofa_ctx* ctx, int timeout_ms, ofa_status_t* status);
+int ofa_steps_done(const ofa_ctx* ctx);                       /* total training steps completed by finished launches */
+float ofa_last_launch_ms(const ofa_ctx* ctx);                 /* CUDA-event time of the last finished launch */
+
+/* live telemetry: the pinned words the device updates while running (doom_job.cuh:29 `Live`, ofa.cu:193,307). */
+typedef struct { unsigned steps; float loss; unsigned decode_steps; } ofa_live_t;
+int ofa_live(const ofa_ctx* ctx, ofa_live_t* out);
+
+/* results: replaces the report section (ofa.cu:722-756). */
+int ofa_read_losses(ofa_ctx* ctx, float* out, size_t n);                  /* loss_hist[0..n) since creation           */
+int ofa_read_step_times(ofa_ctx* ctx, unsigned long long* out, size_t n); /* %globaltimer ns at the end of each step of the last launch */
+int ofa_num_phases(const ofa_ctx* ctx);
+int ofa_phase_info(const ofa_ctx* ctx, int phase, char* name, size_t name_cap, int* kind, int* ntasks, unsigned long long* busy_ns);
+int ofa_decode_steps(const ofa_ctx* ctx);                                  /* tokens processed by the serving job      */
+int ofa_read_decode_tokens(ofa_ctx* ctx, int* out, size_t cap);            /* the pinned ring: sampled ids, OFA_OUT_* markers, -1 = unused */
+int ofa_read_decode_logits(ofa_ctx* ctx, float* out, size_t n);            /* fp32 logits of the last decoded token    */
+#define OFA_OUT_RESTART (1 << 24)
+#define OFA_OUT_FORCED ((1 << 24) + 1)
+/* named activation / gradient buffers for parity checks: "logits","lnf","x<l>","qkv<l>","att<l>","dx<l>", ... */
+int ofa_read_buffer(ofa_ctx* ctx, const char* name, void* out, size_t bytes);
+
+/* data-parallel hooks (no counterpart in the single-GPU reference): the gradient buffer (bf16 when grad_bf16, else fp32),
+ * its buckets, and the two device flag arrays (int32 per bucket). The communication side waits until ready[b] >= s+1,
+ * all-reduces bucket b in place, then stores s+1 to done[b], for every step s of a launch (flags restart at 0 per launch). */
+int ofa_num_buckets(const ofa_ctx* ctx);
+int ofa_bucket_span(const ofa_ctx* ctx, int bucket, size_t* offset, size_t* count);   /* elements */
+void* ofa_grad_buffer(const ofa_ctx* ctx);
+int* ofa_ext_ready_flags(const ofa_ctx* ctx);
+int* ofa_ext_done_flags(const ofa_ctx* ctx);
+
+/* ---- task level -------------------------------------------------------------------------------------------------- */
+enum {  /* task kinds, = TaskKind of the device code */
+  OFA_TK_DATA = 0, OFA_TK_EMBED, OFA_TK_LN_FWD, OFA_TK_GEMM, OFA_TK_ATT_FWD, OFA_TK_ATT_PREP, OFA_TK_ATT_BWD, OFA_TK_CE,
+  OFA_TK_CE_MEAN, OFA_TK_LN_BWD, OFA_TK_LN_DG, OFA_TK_EMB_WTE, OFA_TK_EMB_WPE, OFA_TK_ADAMW, OFA_TK_BARRIER
+};
+enum { OFA_GEMM_NN = 0, OFA_GEMM_NT = 1, OFA_GEMM_TN = 2 };
+enum { OFA_EPI_STORE = 0, OFA_EPI_RES = 1, OFA_EPI_GELU = 2, OFA_EPI_DGELU = 3, OFA_EPI_F32 = 4 };
+
+/* One phase = ntasks independent block-sized tasks (PhaseDesc, ofa.cu:89-95). Pointers are DEVICE pointers obtained
+ * from ofa_dev_alloc. For GEMM phases ntasks/tiles are derived from M,N,K and the TMA descriptors are built here. */
+typedef struct {
+  int kind, layout, epi, accumulate;
+  int M, N, K, lda, ldb, ldc, ldaux, nsub;
+  void* p[10];              /* GEMM: p[0]=A p[1]=B p[2]=C p[3]=aux; other kinds: the argument order of the device task */
+  size_t n;
+  int i0, i1, i2;
+} ofa_phase;
+
+typedef struct { int vocab, d_model, n_layer, n_head, ctx_len, batch; } ofa_dims;
+
+int ofa_dev_alloc(void** p, size_t bytes);          /* zero-filled */
+int ofa_dev_free(void* p);
+int ofa_h2d(void* dst, const void* src, size_t bytes);
+int ofa_d2h(void* dst, const void* src, size_t bytes);
+/* Runs phases[0..nph) as a chain (phase i waits for phase i-1; phase 0 of repeat r waits for the last phase of r-1),
+ * `repeats` times, in one persistent launch on all SMs. ms = CUDA-event time of the launch. AdamW phases use `adam`
+ * = {lr, beta1, beta2, eps, wd, grad_scale} with optimizer step r+1. */
+int ofa_run_phases(int dtype, const ofa_dims* dims, const ofa_phase* phases, int nph, int repeats, const float* adam,
+                   float* ms, ofa_status_t* status);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,435 @@
+// Memory-bound training tasks: embedding forward/backward, LayerNorm forward/backward (+dgamma reduce), softmax
+// cross-entropy with in-place dlogits, mean loss, and the fused AdamW. Every task is templated on the activation storage
+// type T (bf16 for GPT-S, float for the tiny model) and, where a row lives in registers, on the model width D.
+//
+// Semantics follow the reference task libraries (llm/elementwise/ew_layernorm.cuh:12-173, ew_loss.cuh:19-192,
+// ew_adamw.cuh:20-67): fp32 statistics, gamma-only LayerNorm with eps 1e-5, two-pass variance, cross-entropy in the exp2
+// domain over the STORED (rounded) logits with dlogits = (softmax - onehot)/N written over the logits, deterministic
+// embedding scatter (contributions added in increasing token index), AdamW with torch's operation order. All reductions
+// have a fixed order, so results do not depend on which block runs which task.
+//
+// Gradient buffers are OVERWRITTEN by their single producer each step (accumulate flags exist for the tied-head case),
+// so AdamW neither reads stale sums nor has to zero the gradient buffer afterwards.
+#pragma once
+#include "common.cuh"
+#include "task_api.h"
+
+namespace ofa {
+namespace ew {
+
+constexpr int ROWS_PER_TASK = 16;    // embed / LayerNorm granularity
+constexpr int CE_ROWS = 4;           // rows per cross-entropy task
+constexpr int EMB_VCHUNK = 128;      // vocabulary rows per embedding-backward task
+constexpr int OPT_CHUNK = 65536;     // elements per AdamW task
+constexpr int WPE_ROWS = 4;          // positions per wpe-backward task
+
+__device__ __forceinline__ void ld4(const float* p, float* f) { ldv(p, f); }
+__device__ __forceinline__ void ld4(const bf16* p, float* f) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x), b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+  f[0] = __bfloat162float(a.x); f[1] = __bfloat162float(a.y); f[2] = __bfloat162float(b.x); f[3] = __bfloat162float(b.y);
+}
+__device__ __forceinline__ void st4(float* p, const float* f) { stv(p, f); }
+__device__ __forceinline__ void st4(bf16* p, const float* f) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
+  uint2 u; u.x = *reinterpret_cast<const uint32_t*>(&a); u.y = *reinterpret_cast<const uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+
+// ---------------------------------------------------------------------------------------------- embedding forward
+// x[r,:] = T(float(wte[tok[r],:]) + float(wpe[r % Tctx,:]));  task = 16 rows.
+template <class T, int D>
+__device__ __forceinline__ void embed_fwd_task(int task, T* x, const T* wte, const T* wpe, const int* tok, int N, int Tctx) {
+  constexpr int VN = Vec<T>::N, VPR = D / VN;
+  static_assert(D % VN == 0, "row must be a whole number of 16-byte vectors");
+  const int r0 = task * ROWS_PER_TASK;
+  for (int i = threadIdx.x; i < ROWS_PER_TASK * VPR; i += NTHR) {
+    const int r = r0 + i / VPR;
+    if (r >= N) break;
+    const int c = (i % VPR) * VN;
+    float a[VN], b[VN];
+    ldv(wte + (size_t)tok[r] * D + c, a);
+    ldv(wpe + (size_t)(r % Tctx) * D + c, b);
+#pragma unroll
+    for (int k = 0; k < VN; k++) a[k] += b[k];
+    stv(x + (size_t)r * D + c, a);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- LayerNorm
+// A warp owns a row; lane l holds vectors l, l+32, ... of the row (NV of them, the tail predicated off for narrow rows).
+template <class T, int D> struct RowRegs {
+  static constexpr int VN = Vec<T>::N;
+  static constexpr int VPR = D / VN;                 // vectors per row
+  static constexpr int NV = (VPR + 31) / 32;         // vectors per lane
+};
+
+// y = (x - mean) * rstd * gamma, saves mean/rstd. Task = 16 rows (warp w: rows w and w+8).
+template <class T, int D>
+__device__ __forceinline__ void ln_fwd_task(int task, T* y, float* mean_o, float* rstd_o, const T* x, const T* gamma, int N) {
+  using R = RowRegs<T, D>;
+  constexpr int VN = R::VN, NV = R::NV;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll 1
+  for (int j = 0; j < 2; j++) {
+    const int r = task * ROWS_PER_TASK + warp + j * 8;
+    if (r >= N) continue;
+    float f[NV][VN];
+    float s = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; v++) {
+      const int vi = v * 32 + lane;
+      if (vi < R::VPR) {
+        ldv(x + (size_t)r * D + vi * VN, f[v]);
+#pragma unroll
+        for (int k = 0; k < VN; k++) s += f[v][k];
+      }
+    }
+    const float mean = warp_sum(s) * (1.f / D);
+    float q = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; v++)
+      if (v * 32 + lane < R::VPR) {
+#pragma unroll
+        for (int k = 0; k < VN; k++) { const float d = f[v][k] - mean; q += d * d; }
+      }
+    const float rstd = rsqrtf(warp_sum(q) * (1.f / D) + 1e-5f);
+#pragma unroll
+    for (int v = 0; v < NV; v++) {
+      const int vi = v * 32 + lane;
+      if (vi < R::VPR) {
+        float g[VN], o[VN];
+        ldv(gamma + vi * VN, g);
+#pragma unroll
+        for (int k = 0; k < VN; k++) o[k] = (f[v][k] - mean) * rstd * g[k];
+        stv(y + (size_t)r * D + vi * VN, o);
+      }
+    }
+    if (lane == 0) { mean_o[r] = mean; rstd_o[r] = rstd; }
+  }
+}
+
+template <int D> __host__ __device__ constexpr size_t ln_bwd_smem_bytes() { return 8 * (size_t)D * sizeof(float); }
+
+// dx = rstd * (g - mean(g) - xhat * mean(g * xhat)) [+ dres],  g = dy * gamma,  xhat = (x - mean) * rstd.
+// Also writes this task's dgamma partial [task, D] = sum over its rows of dy * xhat (8 warps summed in index order).
+template <class T, int D>
+__device__ __forceinline__ void ln_bwd_task(int task, T* dx, float* dgamma_part, const T* dy, const T* x, const float* mean,
+                                            const float* rstd, const T* gamma, const T* dres, int N, unsigned char* smem) {
+  using R = RowRegs<T, D>;
+  constexpr int VN = R::VN, NV = R::NV;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* sdg = reinterpret_cast<float*>(smem);   // [8][D]
+  float gam[NV][VN], dg[NV][VN];
+#pragma unroll
+  for (int v = 0; v < NV; v++) {
+    const int vi = v * 32 + lane;
+    if (vi < R::VPR) ldv(gamma + vi * VN, gam[v]);
+#pragma unroll
+    for (int k = 0; k < VN; k++) dg[v][k] = 0.f;
+  }
+#pragma unroll 1
+  for (int j = 0; j < 2; j++) {
+    const int r = task * ROWS_PER_TASK + warp + j * 8;
+    if (r >= N) continue;
+    const float mu = mean[r], rs = rstd[r];
+    float xh[NV][VN], g[NV][VN];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; v++) {
+      const int vi = v * 32 + lane;
+      if (vi < R::VPR) {
+        float dyv[VN];
+        ldv(x + (size_t)r * D + vi * VN, xh[v]);
+        ldv(dy + (size_t)r * D + vi * VN, dyv);
+#pragma unroll
+        for (int k = 0; k < VN; k++) {
+          xh[v][k] = (xh[v][k] - mu) * rs;
+          g[v][k] = dyv[k] * gam[v][k];
+          s1 += g[v][k]; s2 += g[v][k] * xh[v][k];
+          dg[v][k] += dyv[k] * xh[v][k];
+        }
+      }
+    }
+    s1 = warp_sum(s1) * (1.f / D); s2 = warp_sum(s2) * (1.f / D);
+#pragma unroll
+    for (int v = 0; v < NV; v++) {
+      const int vi = v * 32 + lane;
+      if (vi < R::VPR) {
+        float o[VN];
+#pragma unroll
+        for (int k = 0; k < VN; k++) o[k] = rs * (g[v][k] - s1 - xh[v][k] * s2);
+        if (dres) {
+          float e[VN]; ldv(dres + (size_t)r * D + vi * VN, e);
+#pragma unroll
+          for (int k = 0; k < VN; k++) o[k] += e[k];
+        }
+        stv(dx + (size_t)r * D + vi * VN, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int v = 0; v < NV; v++) {
+    const int vi = v * 32 + lane;
+    if (vi < R::VPR) {
+#pragma unroll
+      for (int k = 0; k < VN; k++) sdg[warp * D + vi * VN + k] = dg[v][k];
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < D; c += NTHR) {
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; w++) s += sdg[w * D + c];
+    dgamma_part[(size_t)task * D + c] = s;
+  }
+  __syncthreads();
+}
+
+// dgamma[c] (=|+=) sum_b part[b, c] in index order. Task = 256 columns. GT = gradient storage type (float, or bf16 bucket).
+template <class GT>
+__device__ __forceinline__ void ln_dgamma_reduce_task(int task, GT* dgamma, const float* part, int nblk, int D, int accumulate) {
+  const int c = task * NTHR + threadIdx.x;
+  if (c < D) {
+    float s = 0.f;
+    for (int b = 0; b < nblk; b++) s += part[(size_t)b * D + c];
+    dgamma[c] = from_f<GT>(accumulate ? to_f(dgamma[c]) + s : s);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- cross-entropy
+// In place: logits[r,:] -> dlogits[r,:] = (softmax - onehot(target)) * inv_n;  loss[r] = logsumexp - logit[target].
+// Pass 1 keeps the row in shared memory (as much as fits in `cache_bytes`), so pass 2 re-reads global memory only for the
+// tail; the bf16 GPT-S row (100,608 B) fits entirely, i.e. the task moves the algorithmic minimum of 2 x row bytes.
+// Task = CE_ROWS rows. Shared memory: 64 B scratch + cache_bytes.
+template <class T>
+__device__ __forceinline__ void ce_task(int task, T* logits, const int* targets, float* loss, int N, int V, float inv_n,
+                                        unsigned char* smem, int cache_bytes) {
+  constexpr int VN = (sizeof(T) == 2) ? 8 : 1;        // fp32 rows (tiny model) are not 16-byte aligned: scalar access
+  constexpr float L2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
+  float* red = reinterpret_cast<float*>(smem);
+  T* cache = reinterpret_cast<T*>(smem + 64);
+  const int t = threadIdx.x;
+  const int nvec = V / VN;
+  const int cvec = min(nvec, cache_bytes / (int)(VN * sizeof(T)));
+  for (int rr = 0; rr < CE_ROWS; rr++) {
+    const int r = task * CE_ROWS + rr;
+    if (r >= N) break;
+    T* row = logits + (size_t)r * V;
+    const int tgt = targets[r];
+    float m = -INFINITY, s = 0.f;
+    for (int v = t; v < nvec; v += NTHR) {
+      float f[VN];
+      if constexpr (VN == 8) {
+        const uint4 u = *reinterpret_cast<const uint4*>(row + (size_t)v * 8);
+        if (v < cvec) *reinterpret_cast<uint4*>(cache + (size_t)v * 8) = u;
+        unpack8(u, f);
+      } else {
+        f[0] = to_f(row[v]);
+        if (v < cvec) cache[v] = row[v];
+      }
+      float cm = f[0];
+#pragma unroll
+      for (int k = 1; k < VN; k++) cm = fmaxf(cm, f[k]);
+      cm *= L2E;
+      if (cm > m) { s *= exp2f(m - cm); m = cm; }
+#pragma unroll
+      for (int k = 0; k < VN; k++) s += exp2f(fmaf(f[k], L2E, -m));
+    }
+    float lt = 0.f;
+    if (t == 0) lt = to_f(row[tgt]);           // read before any thread overwrites the row (ordered by the syncs below)
+    const float M = block_max(m, red);
+    const float S = block_sum(s * exp2f(m - M), red);
+    if (t == 0) loss[r] = M * LN2 + logf(S) - lt;
+    const float invS = 1.f / S;
+    for (int v = t; v < nvec; v += NTHR) {
+      float f[VN];
+      if constexpr (VN == 8) {
+        const uint4 u = (v < cvec) ? *reinterpret_cast<const uint4*>(cache + (size_t)v * 8) : *reinterpret_cast<const uint4*>(row + (size_t)v * 8);
+        unpack8(u, f);
+      } else {
+        f[0] = (v < cvec) ? to_f(cache[v]) : to_f(row[v]);
+      }
+#pragma unroll
+      for (int k = 0; k < VN; k++) {
+        float p = exp2f(fmaf(f[k], L2E, -M)) * invS;
+        if (v * VN + k == tgt) p -= 1.f;
+        f[k] = p * inv_n;
+      }
+      if constexpr (VN == 8) *reinterpret_cast<uint4*>(row + (size_t)v * 8) = pack8(f);
+      else row[v] = from_f<T>(f[0]);
+    }
+    __syncthreads();   // cache and scratch are reused by the next row
+  }
+}
+
+// mean_loss[0] = (sum_r loss[r]) / N, fixed order. One task.
+__device__ __forceinline__ float ce_mean_task(float* mean_loss, const float* loss, int N, unsigned char* smem) {
+  float s = 0.f;
+  for (int i = threadIdx.x; i < N; i += NTHR) s += loss[i];
+  s = block_sum(s, reinterpret_cast<float*>(smem));
+  const float m = s / (float)N;
+  if (threadIdx.x == 0) mean_loss[0] = m;
+  return m;
+}
+
+// ---------------------------------------------------------------------------------------------- embedding backward
+__host__ __device__ constexpr size_t embed_bwd_wte_smem_bytes(int N) { return 1024 + 5 * (size_t)N; }
+
+// dwte32[v,:] (=|+=) sum over tokens n with tok[n] == v of dx0[n,:], added in increasing n. Task = 128 vocabulary rows:
+// the block scans all N tokens, compacts the matches in token order, then each warp owns rows w, w+8, ... and accumulates
+// their tokens in registers. Without `accumulate` every row of the chunk is written (zeros where the token is absent), so
+// the gradient buffer needs no clearing between steps.
+template <class T, int D, class GT>
+__device__ __noinline__ void embed_bwd_wte_task(int task, GT* dwte32, const T* dx0, const int* tok, int N, int V, int accumulate,
+                                                unsigned char* smem) {
+  using R = RowRegs<T, D>;
+  constexpr int VN = R::VN, NV = R::NV;                // lane owns 16-byte vectors lane, lane+32, ... of a row
+  int* cnt = reinterpret_cast<int*>(smem);           // [256]
+  int* list = reinterpret_cast<int*>(smem + 1024);   // [N] token positions, in order
+  unsigned char* rowof = smem + 1024 + 4 * (size_t)N;  // [N] row within the chunk
+  const int t = threadIdx.x, lo = task * EMB_VCHUNK;
+  const int per = (N + NTHR - 1) / NTHR, a = t * per, b = min(N, a + per);
+  int c = 0;
+  for (int n = a; n < b; n++) { const int v = tok[n] - lo; c += (unsigned)v < (unsigned)EMB_VCHUNK; }
+  cnt[t] = c;
+  __syncthreads();
+  int off = 0, total = 0;
+  for (int i = 0; i < NTHR; i++) { const int x = cnt[i]; if (i < t) off += x; total += x; }
+  for (int n = a; n < b; n++) {
+    const int v = tok[n] - lo;
+    if ((unsigned)v < (unsigned)EMB_VCHUNK) { list[off] = n; rowof[off] = (unsigned char)v; off++; }
+  }
+  __syncthreads();
+  const int warp = t >> 5, lane = t & 31;
+  for (int r = warp; r < EMB_VCHUNK; r += NTHR / 32) {
+    if (lo + r >= V) break;
+    float acc[NV][VN];
+    GT* dst = dwte32 + (size_t)(lo + r) * D;
+#pragma unroll
+    for (int v = 0; v < NV; v++) {
+      const int vi = v * 32 + lane;
+#pragma unroll
+      for (int k = 0; k < VN; k++) acc[v][k] = (accumulate && vi < R::VPR) ? to_f(dst[vi * VN + k]) : 0.f;
+    }
+    for (int k0 = 0; k0 < total; k0 += 32) {
+      const int k = k0 + lane;
+      unsigned m = __ballot_sync(0xffffffffu, k < total && rowof[k] == r);
+      while (m) {
+        const int n = list[k0 + __ffs(m) - 1]; m &= m - 1;
+        const T* src = dx0 + (size_t)n * D;
+#pragma unroll
+        for (int v = 0; v < NV; v++) {
+          const int vi = v * 32 + lane;
+          if (vi < R::VPR) {
+            float f[VN]; ldv(src + vi * VN, f);
+#pragma unroll
+            for (int kk = 0; kk < VN; kk++) acc[v][kk] += f[kk];
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int v = 0; v < NV; v++) {
+      const int vi = v * 32 + lane;
+      if (vi < R::VPR) {
+#pragma unroll
+        for (int k = 0; k < VN; k += 4) st4(dst + vi * VN + k, &acc[v][k]);
+      }
+    }
+  }
+  __syncthreads();
+}
+
+// dwpe32[p,:] (=) sum_b dx0[b*Tctx + p,:], b increasing. Task = 4 positions.
+template <class T, class GT>
+__device__ __forceinline__ void embed_bwd_wpe_task(int task, GT* dwpe32, const T* dx0, int N, int Tctx, int D) {
+  for (int pp = 0; pp < WPE_ROWS; pp++) {
+    const int p = task * WPE_ROWS + pp;
+    if (p >= Tctx) break;
+    for (int c = threadIdx.x; c < D; c += NTHR) {
+      float s = 0.f;
+      for (int n = p; n < N; n += Tctx) s += to_f(dx0[(size_t)n * D + c]);
+      dwpe32[(size_t)p * D + c] = from_f<GT>(s);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- AdamW
+struct AdamHP { float lr, beta1, beta2, eps, weight_decay, grad_scale; int step; };   // step is 1-based
+
+__device__ __forceinline__ float lr_at(const AdamConst& h, int s) {
+  if (h.constant_lr) return h.lr_max;
+  if (s < h.warmup) return h.lr_max * (float)(s + 1) / (float)h.warmup;
+  const double p = (double)(s - h.warmup) / (double)(h.sched_steps - h.warmup);
+  const double q = p < 1.0 ? p : 1.0;
+  return (float)(h.lr_min + 0.5 * (h.lr_max - h.lr_min) * (1.0 + cos(3.14159265358979323846 * q)));
+}
+__device__ __forceinline__ AdamHP adam_hp(const AdamConst& h, int step) {
+  AdamHP hp; hp.lr = lr_at(h, step); hp.beta1 = h.beta1; hp.beta2 = h.beta2; hp.eps = h.eps; hp.weight_decay = h.wd;
+  hp.grad_scale = h.grad_scale; hp.step = step + 1; return hp;
+}
+
+// torch.optim.AdamW (non-fused, non-amsgrad) operation order on fp32 master weights:
+//   p *= 1 - lr*wd (unless the element lies in a no-decay range) ; m += (g - m)(1 - b1) ; v = fma(v, b2, (1 - b2) g^2) ;
+//   p -= lr/(1 - b1^t) * m / (sqrt(v)/sqrt(1 - b2^t) + eps)          (bias corrections in double)
+// then refreshes the working copy Wact (type T) that forward, backward and the decoder read. The gradient is read as GT
+// (fp32 single-GPU buffer, or the all-reduced bf16 bucket) and multiplied by hp.grad_scale (1/world size).
+// nodecay: sorted disjoint [start,end) element ranges relative to W. Task = 65,536 elements; n and ranges multiples of 4.
+template <class T, class GT>
+__device__ __forceinline__ void adamw_task(int task, float* W, const GT* G, float* M, float* Vv, T* Wact, size_t n, AdamHP hp,
+                                           const int2* nodecay, int n_nodecay) {
+  const size_t cs = (size_t)task * OPT_CHUNK;
+  if (cs >= n) return;
+  const size_t ce = cs + OPT_CHUNK < n ? cs + OPT_CHUNK : n;
+  const double bc1 = 1.0 - pow((double)hp.beta1, (double)hp.step);
+  const double bc2 = 1.0 - pow((double)hp.beta2, (double)hp.step);
+  const float step_size = (float)((double)hp.lr / bc1);
+  const float inv_sqrt_bc2 = (float)(1.0 / sqrt(bc2));
+  const float decay_mul = 1.f - hp.lr * hp.weight_decay;
+  const float omb1 = 1.f - hp.beta1, omb2 = 1.f - hp.beta2;
+  const float gs = hp.grad_scale;
+  int lo = 0;
+  {  // first range whose end lies beyond the chunk start
+    int hi = n_nodecay;
+    while (lo < hi) { const int mid = (lo + hi) >> 1; if ((size_t)nodecay[mid].y <= cs) lo = mid + 1; else hi = mid; }
+  }
+  const bool any_nd = lo < n_nodecay && (size_t)nodecay[lo].x < ce;
+#pragma unroll 2
+  for (size_t i = cs + (size_t)threadIdx.x * 4; i < ce; i += NTHR * 4) {
+    float w[4], g[4], m[4], v[4];
+    ld4(W + i, w); ld4(G + i, g); ld4(M + i, m); ld4(Vv + i, v);
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+      bool dec = true;
+      if (any_nd) {
+        const int idx = (int)(i + k);
+        int ri = lo;
+        while (ri < n_nodecay && nodecay[ri].y <= idx) ri++;
+        if (ri < n_nodecay && idx >= nodecay[ri].x) dec = false;
+      }
+      const float gg = g[k] * gs;
+      const float p = dec ? w[k] * decay_mul : w[k];
+      m[k] = m[k] + (gg - m[k]) * omb1;
+      v[k] = fmaf(v[k], hp.beta2, omb2 * gg * gg);
+      const float denom = sqrtf(v[k]) * inv_sqrt_bc2 + hp.eps;
+      w[k] = p - step_size * (m[k] / denom);
+    }
+    st4(W + i, w); st4(M + i, m); st4(Vv + i, v); st4(Wact + i, w);
+  }
+}
+
+// tok_in / tok_tgt for sequence `seq` of step `step`: window start from the table, or a counter-based hash of the seed.
+__device__ __forceinline__ void data_task(int seq, int step, const uint32_t* data, u64 ntok, const uint32_t* starts, int nstarts,
+                                          u64 seed, int* tok_in, int* tok_tgt, int Tctx, int B) {
+  u64 st;
+  if (starts) st = starts[(size_t)(step % nstarts) * B + seq];
+  else st = splitmix64(seed ^ ((u64)step * B + seq)) % (ntok - Tctx - 1);
+  for (int t = threadIdx.x; t < Tctx; t += NTHR) {
+    tok_in[seq * Tctx + t] = (int)data[st + t];
+    tok_tgt[seq * Tctx + t] = (int)data[st + t + 1];
+  }
+}
+
+}  // namespace ew
+}  // namespace ofa

@@ -1,0 +1,255 @@
+// The persistent kernel: one launch, blocks that never exit until their job is finished, on-GPU ticket queues with
+// dependency counters, and a static split of the SMs between the training job, the serving (decode) job and a reserved
+// idle partition.
+//
+// Scheduling model (same contract as the reference's job_loop / ofa_kernel, llm/b200/megakernel/ofa.cu:220-326):
+//   thread 0 of a block takes the next ticket g of its job with one fetch-add; g -> (step, phase, task) through the prefix
+//   table; it then waits until every dependency (phase p, step delta d) satisfies done[p] >= ntasks[p]*(step+1+d); the
+//   whole block runs the task; after a device-scope fence thread 0 bumps done[phase]. Phases are topologically ordered and
+//   cross-step dependencies point backwards, so every dependency is a lower ticket and the lowest unfinished ticket is
+//   always runnable: no deadlock as long as every claimed ticket is eventually run, which holds because a block holds at
+//   most one ticket.
+// What differs from the reference: the phase lookup is a binary search; every wait is bounded (%globaltimer deadline and a
+// grid-wide abort word) so that a wedged task makes the kernel RETURN with a status instead of hanging the GPU; the
+// per-block tensor-core state (mbarriers, TMEM) is created once per block, not per task; external (host / other-rank)
+// events enter the graph as ordinary 1-task phases (TK_EXT_WAIT / TK_EXT_SIGNAL).
+#pragma once
+#include "common.cuh"
+#include "task_api.h"
+#include "elementwise.cuh"
+#include "gemm_tc.cuh"
+#include "attn_mma.cuh"
+#include "simt_f32.cuh"
+#include "decode.cuh"
+#include <type_traits>
+
+namespace ofa {
+
+template <class T> struct IsBf16 { static constexpr bool value = std::is_same<T, bf16>::value; };
+
+// ---------------------------------------------------------------------------------------------- one training task
+template <class T, int D, int DH>
+__device__ __forceinline__ void run_train_task(const Ctx& C, const PhaseDesc& d, int ph, int local, int step, unsigned char* smem,
+                                               gemm_tc::GemmPipe& gp) {
+  const ModelDims& md = C.md;
+  switch (d.kind) {
+    case TK_DATA:
+      ew::data_task(local, step + C.step_base, C.data, C.ntok, C.starts, C.nstarts, C.seed, C.tok_in, C.tok_tgt, md.T, md.B);
+      break;
+    case TK_EMBED:
+      ew::embed_fwd_task<T, D>(local, (T*)d.p[0], (const T*)d.p[1], (const T*)d.p[2], (const int*)d.p[3], md.N, md.T);
+      break;
+    case TK_LN_FWD:
+      ew::ln_fwd_task<T, D>(local, (T*)d.p[0], (float*)d.p[1], (float*)d.p[2], (const T*)d.p[3], (const T*)d.p[4], md.N);
+      break;
+    case TK_GEMM:
+      if constexpr (IsBf16<T>::value) gemm_tc::run(d, local, smem, gp, C.status, ph);
+      else f32::gemm_run(d, local, smem);
+      break;
+    case TK_ATT_FWD: {
+      if constexpr (IsBf16<T>::value) {
+        const int BH = md.B * md.H, QT = md.T / attn::QTILE;
+        const int qt = QT - 1 - local / BH, bh = local % BH;      // heavy (late) query tiles first
+        attn::fwd_task((const bf16*)d.p[0], (bf16*)d.p[1], (float*)d.p[2], bh / md.H, bh % md.H, qt, md.T, md.H, smem);
+      } else {
+        f32::attn_fwd_task<DH>((const float*)d.p[0], (float*)d.p[1], (float*)d.p[2], local / md.H, local % md.H, md.T, md.H, smem);
+      }
+      break;
+    }
+    case TK_ATT_PREP: {
+      if constexpr (IsBf16<T>::value) {
+        const int BH = md.B * md.H;
+        const int rt = local / BH, bh = local % BH;
+        attn::bwd_prep_task((const bf16*)d.p[0], (const bf16*)d.p[1], (float*)d.p[2], bh / md.H, bh % md.H, rt, md.T, md.H);
+      }
+      break;
+    }
+    case TK_ATT_BWD: {
+      if constexpr (IsBf16<T>::value) {
+        const int BH = md.B * md.H, QT = md.T / attn::QTILE;
+        if (local < BH * QT) {                                     // dK/dV: early key tiles see the most queries -> first
+          const int kt = local / BH, bh = local % BH;
+          attn::bwd_dkdv_task((const bf16*)d.p[0], (const bf16*)d.p[1], (const float*)d.p[2], (const float*)d.p[3], (bf16*)d.p[4],
+                              bh / md.H, bh % md.H, kt, md.T, md.H, smem);
+        } else {                                                   // dQ: late query tiles see the most keys -> first
+          const int l2 = local - BH * QT, qt = QT - 1 - l2 / BH, bh = l2 % BH;
+          attn::bwd_dq_task((const bf16*)d.p[0], (const bf16*)d.p[1], (const float*)d.p[2], (const float*)d.p[3], (bf16*)d.p[4],
+                            bh / md.H, bh % md.H, qt, md.T, md.H, smem);
+        }
+      } else {
+        f32::attn_bwd_task<DH>((const float*)d.p[0], (const float*)d.p[5], (const float*)d.p[1], (const float*)d.p[2], (float*)d.p[4],
+                               local / md.H, local % md.H, md.T, md.H, smem);
+      }
+      break;
+    }
+    case TK_CE:
+      ew::ce_task<T>(local, (T*)d.p[0], (const int*)d.p[1], (float*)d.p[2], md.N, md.V, 1.0f / (float)md.N, smem, d.i0);
+      break;
+    case TK_CE_MEAN: {
+      const float lv = ew::ce_mean_task((float*)d.p[0], (const float*)d.p[1], md.N, smem);
+      if (threadIdx.x == 0) { C.loss_hist[step] = lv; if (C.live) C.live->loss = lv; }
+      break;
+    }
+    case TK_LN_BWD:
+      ew::ln_bwd_task<T, D>(local, (T*)d.p[0], (float*)d.p[1], (const T*)d.p[2], (const T*)d.p[3], (const float*)d.p[4],
+                            (const float*)d.p[5], (const T*)d.p[6], (const T*)d.p[7], md.N, smem);
+      break;
+    case TK_LN_DG:
+      if (d.i1) ew::ln_dgamma_reduce_task<bf16>(local, (bf16*)d.p[0], (const float*)d.p[1], (md.N + ew::ROWS_PER_TASK - 1) / ew::ROWS_PER_TASK, D, d.i0);
+      else ew::ln_dgamma_reduce_task<float>(local, (float*)d.p[0], (const float*)d.p[1], (md.N + ew::ROWS_PER_TASK - 1) / ew::ROWS_PER_TASK, D, d.i0);
+      break;
+    case TK_EMB_WTE:
+      if (d.i1) ew::embed_bwd_wte_task<T, D, bf16>(local, (bf16*)d.p[0], (const T*)d.p[1], (const int*)d.p[2], md.N, md.V, d.i0, smem);
+      else ew::embed_bwd_wte_task<T, D, float>(local, (float*)d.p[0], (const T*)d.p[1], (const int*)d.p[2], md.N, md.V, d.i0, smem);
+      break;
+    case TK_EMB_WPE:
+      if (d.i1) ew::embed_bwd_wpe_task<T, bf16>(local, (bf16*)d.p[0], (const T*)d.p[1], md.N, md.T, D);
+      else ew::embed_bwd_wpe_task<T, float>(local, (float*)d.p[0], (const T*)d.p[1], md.N, md.T, D);
+      break;
+    case TK_ADAMW: {
+      const ew::AdamHP hp = ew::adam_hp(C.hp, step + C.step_base);
+      if (d.i1) ew::adamw_task<T, bf16>(local, (float*)d.p[0], (const bf16*)d.p[1], (float*)d.p[2], (float*)d.p[3], (T*)d.p[4], d.n, hp, (const int2*)d.p[5], d.i0);
+      else ew::adamw_task<T, float>(local, (float*)d.p[0], (const float*)d.p[1], (float*)d.p[2], (float*)d.p[3], (T*)d.p[4], d.n, hp, (const int2*)d.p[5], d.i0);
+      break;
+    }
+    case TK_EXT_SIGNAL:
+      if (threadIdx.x == 0) { __threadfence_system(); *reinterpret_cast<volatile int*>(d.p[0]) = step + 1; __threadfence_system(); }
+      break;
+    case TK_EXT_WAIT:
+      if (threadIdx.x == 0) {
+        const volatile int* flag = reinterpret_cast<const volatile int*>(d.p[0]);
+        const u64 t0 = gtimer();
+        while (*flag < step + 1) {
+          if (aborted(C.status)) break;
+          if (gtimer() - t0 > C.dep_timeout_ns) { raise_abort(C.status, ST_EXTERNAL_TIMEOUT, ph, local, step); break; }
+          __nanosleep(200);
+        }
+        __threadfence_system();
+      }
+      break;
+    default: break;   // TK_BARRIER
+  }
+}
+
+template <class T, int D, int DH>
+__device__ __forceinline__ void run_decode_task(const Ctx& C, const PhaseDesc& d, int local, unsigned char* smem) {
+  switch (d.kind) {
+    case TK_DEC_QKV: dec::task_qkv<T, D, DH>(C.dp, C.md, d.i0, local, smem); break;
+    case TK_DEC_ATTWO: dec::task_attwo<T, D, DH>(C.dp, C.md, d.i0, local, smem); break;
+    case TK_DEC_UPDN: dec::task_updn<T, D, DH>(C.dp, C.md, d.i0, local, smem); break;
+    case TK_DEC_HEAD: dec::task_head<T, D, DH>(C.dp, C.md, local, smem); break;
+    case TK_DEC_SAMPLE: dec::task_sample<T, D, DH>(C.dp, C.md, C.live, smem); break;
+    default: break;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- scheduler
+template <class T, int D, int DH>
+__device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* smem) {
+  volatile int* s_sel = reinterpret_cast<volatile int*>(smem + C.smem_bytes - 128);   // the last 256 bytes of dynamic shared memory are the block's control area
+  const int tid = threadIdx.x;
+  u64 busy = 0;
+  int rstep = -1, rph = -1;                         // thread 0: the (step, phase) last seen ready
+  const unsigned total = (unsigned)J.nsteps * (unsigned)J.tasks_per_step;
+  gemm_tc::GemmPipe gp; gp.stage_count = gp.tile_count = gp.tmem_base = 0;
+  const bool use_tc = IsBf16<T>::value && job_id == 0;
+  if (use_tc) gemm_tc::block_init(gp, smem, C.status);
+  for (;;) {
+    if (tid == 0) {
+      int res = 0, step = 0, ph = 0, local = 0;
+      if (aborted(C.status) || (job_id == 1 && C.use_train && ld_relaxed(C.finished))) res = -2;
+      else {
+        const unsigned g = atomicAdd(J.ticket, 1u);
+        if (g >= total) res = -2;
+        else {
+          step = (int)(g / (unsigned)J.tasks_per_step);
+          const int r = (int)(g - (unsigned)step * (unsigned)J.tasks_per_step);
+          int lo = 0, hi = J.nph;                   // last phase whose prefix <= r
+          while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if (__ldg(J.prefix + mid) <= r) lo = mid; else hi = mid; }
+          ph = lo; local = r - __ldg(J.prefix + ph);
+          if (!(step == rstep && ph == rph)) {
+            const int off = __ldg(J.dep_off + ph), cnt = __ldg(J.dep_cnt + ph);
+            const u64 t0 = gtimer();
+            unsigned spins = 0;
+            for (;;) {
+              bool ready = true;
+              for (int k = 0; k < cnt && ready; k++) {
+                const Dep e = J.deps[off + k];
+                const int need = __ldg(J.ntasks + e.phase) * (step + 1 + e.delta);
+                if (need > 0 && ld_acquire(J.done + e.phase) < need) ready = false;
+              }
+              if (ready) { rstep = step; rph = ph; break; }
+              if (job_id == 1 && C.use_train && ld_relaxed(C.finished)) { res = -2; break; }
+              if ((++spins & 63u) == 0) {
+                if (aborted(C.status)) { res = -2; break; }
+                if (gtimer() - t0 > C.dep_timeout_ns) { raise_abort(C.status, ST_DEP_TIMEOUT, ph, local, step); res = -2; break; }
+              }
+              __nanosleep(job_id == 1 ? 40 : 80);
+            }
+          }
+        }
+      }
+      s_sel[0] = res; s_sel[1] = step; s_sel[2] = ph; s_sel[3] = local;
+    }
+    __syncthreads();
+    const int res = s_sel[0], step = s_sel[1], ph = s_sel[2], local = s_sel[3];
+    __syncthreads();
+    if (res < 0) break;
+    const PhaseDesc& d = J.ph[ph];
+    u64 t0 = 0;
+    if (tid == 0) t0 = gtimer();
+    if (job_id == 0) run_train_task<T, D, DH>(C, d, ph, local, step, smem, gp);
+    else run_decode_task<T, D, DH>(C, d, local, smem);
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      const u64 t1 = gtimer();
+      busy += t1 - t0;
+      if (job_id == 0 && C.phase_busy) {
+        atomicAdd(C.phase_busy + ph, t1 - t0);
+        if (step == C.prof_step) { atomicMin(C.phase_first + ph, t0); atomicMax(C.phase_last + ph, t1); }
+      }
+      const int old = atomicAdd(J.done + ph, 1);
+      if (ph == J.last_phase && old == __ldg(J.ntasks + ph) * (step + 1) - 1) {     // last task of the step
+        if (job_id == 0) {
+          C.step_done[step] = t1;
+          if (C.live) C.live->steps = (unsigned)(step + 1);
+          if (step == J.nsteps - 1) { *C.t_end = t1; __threadfence(); atomicExch(C.finished, 1); }
+        }
+      }
+    }
+  }
+  if (use_tc) gemm_tc::block_exit(gp, smem, C.status);
+  if (tid == 0 && C.blk_busy) C.blk_busy[blockIdx.x * 2 + job_id] = busy;
+}
+
+// Role of a block = the partition its SM falls into: [0, infer) serve, [infer, infer+reserved) idle (left free for
+// collectives), the next train_sms train, the rest idle.
+template <class T, int D, int DH>
+__global__ void __launch_bounds__(NTHR, 2) ofa_kernel(const __grid_constant__ Ctx C) {
+  extern __shared__ __align__(1024) unsigned char dsm[];
+  const unsigned hw = smid();
+  const int rank = C.smid_rank ? C.smid_rank[hw] : (int)hw;
+  const int isms = C.use_decode ? C.infer_sms : 0;
+  if (rank < isms) job_loop<T, D, DH>(C, C.dec, 1, dsm);
+  else if (rank < isms + C.reserved_sms) return;
+  else if (rank < isms + C.reserved_sms + C.train_sms) { if (C.use_train) job_loop<T, D, DH>(C, C.train, 0, dsm); }
+}
+
+// one resident block per slot records its %smid so the host can build a dense rank table
+__global__ void __launch_bounds__(NTHR, 2) smid_probe_kernel(unsigned* seen) {
+  extern __shared__ __align__(1024) unsigned char dsm[];
+  if (threadIdx.x == 0) {
+    const unsigned id = smid();
+    atomicOr(&seen[id >> 5], 1u << (id & 31));
+    const u64 t0 = gtimer();
+    while (gtimer() - t0 < 2000000ull) {}      // 2 ms: keeps the block resident so that every SM receives its share
+    dsm[0] = 0;
+  }
+}
+
+// first embedding of a decode context: xw := fx(wte[token] + wpe[pos])
+template <class T, int D>
+__global__ void decode_init_embed_kernel(DecodeParams P) { dec::write_embed<T, D>(P, P.st.scal[DS_TOKEN], P.st.scal[DS_POS]); }
+
+}  // namespace ofa

@@ -1,0 +1,141 @@
+// The task API of the megakernel: what a phase is, how a job (a cyclic table of phases with dependency counters) is laid
+// out in device memory, and the context the one persistent launch receives. Shared by host (graph builder) and device.
+//
+// It keeps the model of the reference program's `PhaseDesc / Job / Ctx` (llm/b200/megakernel/ofa.cu:87-117): a phase is
+// `ntasks` independent block-sized tasks of one kind; a job is the list of phases of one step, executed for `nsteps`
+// steps; a global ticket counter hands out (step, phase, task) in topological order; `done[phase]` counts finished tasks
+// monotonically over all steps, and a dependency (phase p, step delta d) of a task in step s is satisfied when
+// done[p] >= ntasks[p] * (s + 1 + d).
+#pragma once
+#include <stdint.h>
+#include <stddef.h>
+
+namespace ofa {
+
+enum TaskKind : int {
+  TK_DATA = 0,     // copy this step's token windows into tok_in / tok_tgt
+  TK_EMBED,        // x0 = wte[tok] + wpe[pos]
+  TK_LN_FWD,
+  TK_GEMM,         // tensor-core (bf16) or SIMT (fp32) GEMM tile strip, see GemmArgs
+  TK_ATT_FWD,
+  TK_ATT_PREP,     // D = rowsum(dO * O)
+  TK_ATT_BWD,      // first half of the tasks: dK/dV, second half: dQ
+  TK_CE,           // in-place logits -> dlogits, per-row loss
+  TK_CE_MEAN,
+  TK_LN_BWD,
+  TK_LN_DG,        // reduce per-task dgamma partials
+  TK_EMB_WTE,
+  TK_EMB_WPE,
+  TK_ADAMW,
+  TK_BARRIER,      // 1 task, does nothing: its completion marks the end of a step
+  TK_DEC_QKV,      // decode job: i0 = layer
+  TK_DEC_ATTWO,
+  TK_DEC_UPDN,
+  TK_DEC_HEAD,
+  TK_DEC_SAMPLE,
+  TK_EXT_WAIT,     // 1 task: wait (bounded) until an external 32-bit flag >= step+1 (gradient all-reduce finished)
+  TK_EXT_SIGNAL,   // 1 task: store step+1 to an external 32-bit flag (gradient bucket ready)
+  TK_COUNT
+};
+
+enum GemmLayout : int { GL_NN = 0, GL_NT = 1, GL_TN = 2 };
+// NN: C[M,N] = A[M,K] . B[K,N]      NT: C = A[M,K] . B[N,K]^T      TN: C = A[K,M]^T . B[K,N]      (all row-major)
+enum GemmEpi : int {
+  GE_STORE = 0,   // C = act(acc)                       (activation storage type)
+  GE_RES,         // C = act(acc + aux)                 (aux may alias C)
+  GE_GELU,        // aux = act(acc); C = act(gelu(aux)) (pre-activation saved for backward)
+  GE_DGELU,       // C = act(acc * gelu'(aux))
+  GE_F32,         // C(fp32) = acc, or C += acc when `accumulate`
+};
+
+struct GemmArgs {
+  const void* A; const void* B; void* C; void* aux;
+  int M, N, K;
+  int lda, ldb, ldc, ldaux;   // leading dimensions in elements
+  int accumulate;             // GE_F32 only
+  int nsub;                   // consecutive 128-wide N tiles handled by one task (tensor-core path)
+  const void* tmA;            // device pointers to the two TMA descriptors (tensor-core path), 64-byte aligned
+  const void* tmB;
+};
+
+struct PhaseDesc {
+  int kind, ntasks, layout, epi;
+  int tiles_m, i0, i1, i2;
+  GemmArgs g;
+  void* p[10];
+  size_t n;
+  float f0, f1;
+};
+
+struct Dep { int phase; int delta; };   // need done[phase] >= ntasks[phase] * (step + 1 + delta)
+
+struct Job {
+  int nph, tasks_per_step, nsteps, last_phase;
+  const PhaseDesc* ph;      // [nph]
+  const int* prefix;        // [nph+1] exclusive prefix sum of ntasks
+  const int* ntasks;        // [nph]
+  const int* dep_off;       // [nph]
+  const int* dep_cnt;       // [nph]
+  const Dep* deps;
+  int* done;                // [nph] monotonically increasing over steps
+  unsigned* ticket;         // next (step * tasks_per_step + task) to hand out
+};
+
+struct ModelDims { int V, D, L, H, T, B, N, FF, DH, valid_vocab; };
+
+struct AdamConst { float lr_max, lr_min, beta1, beta2, eps, wd; int warmup, sched_steps, constant_lr; float grad_scale; };
+
+// pinned, host-mapped words the device updates while running; any host thread may read them
+struct Live { unsigned steps; float loss; unsigned dec_steps; unsigned pad; };
+
+constexpr int OUT_RESTART = 1 << 24;       // out_tokens marker: a new answer starts (prompt about to be fed)
+constexpr int OUT_FORCED = OUT_RESTART + 1; // out_tokens marker: a prompt token was fed (no sample kept)
+
+struct DecodeState {       // device memory; fixed-point residual makes the task order irrelevant to the result
+  unsigned long long* xw;  // [D] residual, int64 in 2^-30 units (master copy)
+  unsigned long long* xr;  // [D] copy read by the MLP task
+  void* q;                 // [D] activation type
+  float* cand_v;           // [2][nchunk]
+  int* cand_i;             // [2][nchunk]
+  int* scal;               // token, pos, step, ctx_full, astep
+  void* kv;                // [L][2][H][T][DH] activation type
+  float* logits;           // [V]
+  int* out_tokens;         // pinned ring [out_cap]
+  int out_cap;
+};
+enum { DS_TOKEN = 0, DS_POS = 1, DS_STEP = 2, DS_CTXFULL = 3, DS_ASTEP = 4 };
+
+struct DecodeParams {
+  // weights: pointers into the SAME working-copy buffer the trainer updates
+  const void *wte, *wpe, *head, *gf;
+  const void* const* wqkv; const void* const* wo; const void* const* wup; const void* const* wdn;
+  const void* const* g1; const void* const* g2;   // device arrays [L]
+  DecodeState st;
+  float temperature;       // <= 0: greedy
+  unsigned long long seed;
+  const int* forced; int nforced;
+  int auto_reset, answer_len;
+  int max_steps;           // stop decoding after this many tokens (0 = until training finishes)
+};
+
+struct DevStatus;
+
+struct Ctx {
+  Job train, dec;
+  ModelDims md;
+  AdamConst hp;
+  const uint32_t* data; unsigned long long ntok; const uint32_t* starts; int nstarts; unsigned long long seed;
+  int* tok_in; int* tok_tgt;
+  int step_base;            // steps completed by earlier launches: added to the step index for data windows, LR and AdamW
+  unsigned long long *phase_busy, *phase_first, *phase_last; int prof_step;
+  unsigned long long* step_done; float* loss_hist; unsigned long long* blk_busy; int* finished; unsigned long long* t_end;
+  int infer_sms, reserved_sms, train_sms, use_decode, use_train;
+  const int* smid_rank;     // %smid -> dense SM rank (nullptr = identity)
+  DecodeParams dp;
+  Live* live;
+  DevStatus* status;
+  unsigned long long dep_timeout_ns;
+  int smem_bytes;           // dynamic shared memory per block; its last 256 bytes hold barriers (tensor-core path) and the scheduler's hand-off words
+};
+
+}  // namespace ofa
