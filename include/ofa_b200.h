@@ -41,7 +41,7 @@ typedef struct {
 } ofa_status_t;
 
 enum { OFA_DTYPE_BF16 = 0, OFA_DTYPE_F32 = 1 };
-enum { OFA_MODE_TRAIN = 0, OFA_MODE_FORWARD = 1, OFA_MODE_NO_OPT = 2 };
+enum { OFA_MODE_TRAIN = 0, OFA_MODE_FORWARD = 1, OFA_MODE_NO_OPT = 2, OFA_MODE_DECODE_ONLY = 3 };
 
 /* Replaces the compile-time constants and argv/env flags of the reference (ofa.cu:61-84, 395-430, 696). */
 typedef struct {
@@ -49,7 +49,7 @@ typedef struct {
   int valid_vocab;          /* ids >= valid_vocab are never sampled (ofa.cu:71 VALID)                             */
   int tied_head;            /* 1: LM head = wte (reference), 0: separate lm_head[V,D] after wpe in the flat layout */
   int dtype;                /* OFA_DTYPE_BF16: d_model 768 / head_dim 64, tensor cores; OFA_DTYPE_F32: d_model 64 / head_dim 16 */
-  int mode;                 /* OFA_MODE_*: full training step, forward through logits only, or forward+backward without AdamW (ofa.cu --no-opt) */
+  int mode;                 /* OFA_MODE_*: full training step; forward through logits only; forward+backward without AdamW (ofa.cu --no-opt); or no training job at all (serving only: ofa_launch counts decode tokens) */
   int sched_steps, warmup, constant_lr;
   float lr_max, lr_min, beta1, beta2, eps, weight_decay;
   unsigned long long data_seed;   /* window starts when no starts table is set (ofa.cu:160) */

@@ -85,7 +85,7 @@ PROTOTYPES = {
 
 OK, TIMEOUT, DEVICE_ABORT, CUDA_ERROR, BAD_CONFIG, BAD_ARGUMENT, NOT_LAUNCHED = range(7)
 DTYPE_BF16, DTYPE_F32 = 0, 1
-MODE_TRAIN, MODE_FORWARD, MODE_NO_OPT = 0, 1, 2
+MODE_TRAIN, MODE_FORWARD, MODE_NO_OPT, MODE_DECODE_ONLY = 0, 1, 2, 3
 (TK_DATA, TK_EMBED, TK_LN_FWD, TK_GEMM, TK_ATT_FWD, TK_ATT_PREP, TK_ATT_BWD, TK_CE, TK_CE_MEAN, TK_LN_BWD, TK_LN_DG, TK_EMB_WTE,
  TK_EMB_WPE, TK_ADAMW, TK_BARRIER) = range(15)
 GEMM_NN, GEMM_NT, GEMM_TN = 0, 1, 2

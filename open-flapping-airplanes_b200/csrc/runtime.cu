@@ -599,7 +599,8 @@ extern "C" int ofa_create(const ofa_config* cfg, ofa_ctx** out) {
   if (cfg->use_decode && (cfg->n_prompt < 1 || cfg->n_prompt > 32)) return bail(OFA_BAD_CONFIG, "decode needs 1..32 prompt tokens");
   if (cfg->use_decode && cfg->n_prompt + cfg->answer_len > m.T && cfg->answer_len > 0) return bail(OFA_BAD_CONFIG, "prompt + answer exceed ctx_len");
   for (int i = 0; i < cfg->n_prompt && cfg->use_decode; i++) if (cfg->prompt[i] < 0 || cfg->prompt[i] >= m.V) return bail(OFA_BAD_CONFIG, "prompt token out of range");
-  if (cfg->mode < 0 || cfg->mode > 2) return bail(OFA_BAD_CONFIG, "bad mode");
+  if (cfg->mode < 0 || cfg->mode > 3) return bail(OFA_BAD_CONFIG, "bad mode");
+  if (cfg->mode == OFA_MODE_DECODE_ONLY && !cfg->use_decode) return bail(OFA_BAD_CONFIG, "decode-only mode needs use_decode");
   if (cfg->dp_world < 1) return bail(OFA_BAD_CONFIG, "dp_world < 1");
 
   c->device = cfg->device;
@@ -615,7 +616,10 @@ extern "C" int ofa_create(const ofa_config* cfg, ofa_ctx** out) {
   // SM split
   int infer = cfg->use_decode ? std::max(0, cfg->infer_sms) : 0, resv = std::max(0, cfg->reserved_sms);
   if (cfg->use_decode && infer == 0) infer = c->num_sms >= 148 ? 24 : std::max(1, c->num_sms / 6);
-  int train = cfg->train_sms > 0 ? cfg->train_sms : c->num_sms - infer - resv;
+  const bool decode_only = cfg->mode == OFA_MODE_DECODE_ONLY;
+  if (decode_only && cfg->infer_sms <= 0) infer = c->num_sms - resv;
+  int train = decode_only ? 0 : (cfg->train_sms > 0 ? cfg->train_sms : c->num_sms - infer - resv);
+  if (!decode_only && train <= 0) return bail(OFA_BAD_CONFIG, "no SMs left for the training job");
   if (infer + resv + train > c->num_sms || train < 0) return bail(OFA_BAD_CONFIG, "SM split exceeds the device's SM count");
 
   c->lay.build(m, cfg->tied_head != 0);
@@ -641,13 +645,13 @@ extern "C" int ofa_create(const ofa_config* cfg, ofa_ctx** out) {
   C.smid_rank = c->d_smid_rank; C.live = c->d_live; C.status = c->d_status; C.finished = c->d_finished; C.t_end = c->d_t_end;
   C.dep_timeout_ns = (unsigned long long)((cfg->timeout_s > 0 ? cfg->timeout_s : 20.0) * 1e9);
   C.prof_step = -1;
-  bool ok = c->bf ? build_train_graph<bf16>(c) : build_train_graph<float>(c);
+  bool ok = decode_only ? true : (c->bf ? build_train_graph<bf16>(c) : build_train_graph<float>(c));
   if (!ok) return bail(OFA_BAD_CONFIG, "training graph: " + c->err);
   if (cfg->use_decode) {
     ok = c->bf ? build_decode_graph<bf16>(c) : build_decode_graph<float>(c);
     if (!ok) return bail(OFA_BAD_CONFIG, "decode graph: " + c->err);
   }
-  const int nph = (int)c->train_ph.size();
+  const int nph = std::max<int>(1, (int)c->train_ph.size());
   c->d_phase_busy = c->ar.alloc<unsigned long long>(nph); c->d_phase_first = c->ar.alloc<unsigned long long>(nph); c->d_phase_last = c->ar.alloc<unsigned long long>(nph);
   c->d_blk_busy = c->ar.alloc<unsigned long long>(2 * c->nblocks);
   if (!c->ar.ok) return bail(OFA_CUDA_ERROR, "out of device memory");
@@ -765,7 +769,7 @@ extern "C" int ofa_launch(ofa_ctx* c, int nsteps) {
   cudaMemsetAsync(c->d_status, 0, sizeof(DevStatus), c->stream);
   cudaMemsetAsync(c->d_finished, 0, sizeof(int), c->stream);
   cudaMemsetAsync(c->d_ext_ready, 0, 64 * sizeof(int), c->stream);
-  cudaMemsetAsync(c->d_phase_busy, 0, sizeof(unsigned long long) * c->train_ph.size(), c->stream);
+  cudaMemsetAsync(c->d_phase_busy, 0, sizeof(unsigned long long) * std::max<size_t>(1, c->train_ph.size()), c->stream);
   C.smem_bytes = c->smem;
   const Ctx& L = C;
   cudaEventRecord(c->ev0, c->stream);

@@ -1,0 +1,184 @@
+"""Model-level parity on the GPU through the C ABI (ofa_create / ofa_launch / ofa_wait / ofa_read_*): the whole training
+step and the live-weight decoder as ONE persistent launch, against the CPU oracle on the same seed and synthetic tokens.
+Bars (BASELINE north star): tiny fp32 model - loss/weights to fp32 rounding and greedy decode token-exact; bf16 model -
+loss within 1e-2 relative, logits max-abs <= 2e-2, gradients per tensor L2 within 2 % / relmax 5e-2
+(llm/b200/megakernel/check_grads.py:14-21); runs are bitwise repeatable (llm/b200/megakernel/check_loss.sh)."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def relmax(a, b):
+    a, b = np.asarray(a, dtype=np.float64), np.asarray(b, dtype=np.float64)
+    return np.abs(a - b).max() / max(np.abs(b).max(), 1e-30)
+
+
+def tiny_setup(ofa, oracle, mode=0, use_decode=0, prompt=None, tied=False, nsteps=3):
+    ocfg = oracle.tiny_config(tied=tied)
+    w0 = oracle.init_weights(ocfg)
+    ntok = 1 << 14
+    tokens = oracle.synthetic_tokens(ocfg.V, ntok, 0)
+    starts = oracle.batch_starts(ocfg, ntok, nsteps)
+    cfg = ofa.default_config("tiny")
+    cfg.mode, cfg.use_decode, cfg.tied_head = mode, use_decode, int(tied)
+    if prompt is not None:
+        for i, t in enumerate(prompt):
+            cfg.prompt[i] = int(t)
+    mk = ofa.Megakernel(cfg)
+    mk.load_weights(oracle.flatten(ocfg, w0))
+    mk.set_tokens(tokens)
+    mk.set_starts(starts.astype(np.uint32))
+    return ocfg, w0, tokens, starts, mk
+
+
+@pytest.mark.parametrize("tied", [False, True])
+def test_tiny_step_matches_oracle(ofa, oracle, tied):
+    ocfg, w0, tokens, starts, mk = tiny_setup(ofa, oracle, tied=tied)
+    ref = oracle.train(ocfg, w0, tokens, starts, 3, precision="fp32", grab_step0=True)
+    mk.run(1)
+    assert abs(mk.losses()[0] - ref["losses"][0]) <= 2e-5 * ref["losses"][0]
+    r1 = oracle.train(ocfg, w0, tokens, starts, 1, precision="fp32")
+    w1 = mk.read_weights()
+    np.testing.assert_allclose(w1, oracle.flatten(ocfg, r1["weights"]), rtol=0, atol=3e-6)
+    # the update moved every weight by about lr: compare the deltas themselves
+    d_gpu = w1 - oracle.flatten(ocfg, w0); d_ref = oracle.flatten(ocfg, r1["weights"]) - oracle.flatten(ocfg, w0)
+    assert relmax(d_gpu, d_ref) <= 2e-2
+    mk.run(2)                                    # a second launch continues the optimizer state and the data windows
+    np.testing.assert_allclose(mk.losses(), ref["losses"], rtol=5e-5)
+    np.testing.assert_allclose(mk.read_weights(), oracle.flatten(ocfg, ref["weights"]), rtol=0, atol=1e-5)
+    assert mk.live()["steps"] == 2 and mk.steps_done == 3
+    mk.close()
+
+
+def test_tiny_gradients_match_oracle(ofa, oracle):
+    ocfg, w0, tokens, starts, mk = tiny_setup(ofa, oracle, mode=ofa.capi.MODE_NO_OPT)
+    ref = oracle.train(ocfg, w0, tokens, starts, 1, precision="fp32", grab_step0=True)
+    mk.run(1)
+    g = mk.read_grads()
+    gref = oracle.flatten(ocfg, ref["grads0"])
+    for name in ["wte", "wpe", "lm_head", "L0.Wqkv", "L0.Wo", "L0.g1", "L1.Wup", "L1.Wdn", "L1.g2", "gf"]:
+        off, cnt = mk.param_span(name)
+        a, b = g[off:off + cnt], gref[off:off + cnt]
+        assert relmax(a, b) <= 2e-4, name
+    np.testing.assert_array_equal(mk.read_weights(), oracle.flatten(ocfg, w0))          # no optimizer in this mode
+    mk.close()
+
+
+def test_tiny_greedy_decode_is_token_exact(ofa, oracle):
+    prompt = [int(t) for t in np.random.default_rng(0).integers(0, 65, size=8)]
+    ocfg, w0, tokens, starts, mk = tiny_setup(ofa, oracle, use_decode=0)
+    mk.run(1)
+    w1_flat = mk.read_weights()
+    mk.close()
+    # decode-only context with the trained weights: 7 forced prompt steps + 64 sampled tokens
+    cfg = ofa.default_config("tiny")
+    cfg.mode, cfg.use_decode, cfg.infer_sms = ofa.capi.MODE_DECODE_ONLY, 1, 32
+    for i, t in enumerate(prompt):
+        cfg.prompt[i] = t
+    dk = None
+    try:
+        dk = ofa.Megakernel(cfg)
+        dk.load_weights(w1_flat)
+        dk.run(7 + 64)
+        out = dk.decode_tokens(128)
+        assert out[0] == ofa.capi.OUT_RESTART and all(t == ofa.capi.OUT_FORCED for t in out[1:7])
+        got = [int(t) for t in out[7:71]]
+        w1 = oracle.unflatten(ocfg, w1_flat)
+        want, last_logits = oracle.greedy_decode(ocfg, w1, prompt, 64)
+        assert got == want
+        assert relmax(dk.decode_logits(), last_logits) <= 1e-4
+        assert dk.decode_steps == 71
+    finally:
+        if dk is not None:
+            dk.close()
+
+
+def small_bf16(ofa, oracle, mode=0, nsteps=5, L=2, V=1024, T=256, B=2, grad_bf16=0):
+    ocfg = oracle.OracleConfig(V=V, D=768, L=L, H=12, T=T, B=B, tied=False)
+    w0 = oracle.init_weights(ocfg)
+    ntok = 1 << 15
+    tokens = oracle.synthetic_tokens(V, ntok, 0)
+    starts = oracle.batch_starts(ocfg, ntok, nsteps)
+    cfg = ofa.default_config("gpt_s")
+    cfg.vocab, cfg.valid_vocab, cfg.n_layer, cfg.ctx_len, cfg.batch, cfg.mode, cfg.grad_bf16 = V, V, L, T, B, mode, grad_bf16
+    mk = ofa.Megakernel(cfg)
+    mk.load_weights(oracle.flatten(ocfg, w0))
+    mk.set_tokens(tokens)
+    mk.set_starts(starts.astype(np.uint32))
+    return ocfg, w0, tokens, starts, mk
+
+
+def test_bf16_logits_match_oracle(ofa, oracle):
+    ocfg, w0, tokens, starts, mk = small_bf16(ofa, oracle, mode=ofa.capi.MODE_FORWARD)
+    mk.run(1)
+    lg = mk.read_buffer("logits", (ocfg.B * ocfg.T, ocfg.V), "bf16")
+    x, _ = oracle.get_batch(ocfg, tokens, starts[0])
+    with torch.no_grad():
+        ref = oracle.GPTOracle(ocfg, w0, "bf16_points").logits(x).reshape(-1, ocfg.V).numpy()
+    assert np.abs(lg - ref).max() <= 2e-2
+    mk.close()
+
+
+@pytest.mark.parametrize("grad_bf16", [0, 1])
+def test_bf16_gradients_match_oracle(ofa, oracle, grad_bf16):
+    ocfg, w0, tokens, starts, mk = small_bf16(ofa, oracle, mode=ofa.capi.MODE_NO_OPT, grad_bf16=grad_bf16)
+    ref = oracle.train(ocfg, w0, tokens, starts, 1, precision="bf16_points", grab_step0=True)
+    mk.run(1)
+    assert abs(mk.losses()[0] - ref["losses"][0]) <= 1e-2 * ref["losses"][0]
+    g = mk.read_grads(); gref = oracle.flatten(ocfg, ref["grads0"])
+    for name in ["wte", "wpe", "lm_head", "gf"] + [f"L{l}.{t}" for l in range(ocfg.L) for t in ("g1", "Wqkv", "Wo", "g2", "Wup", "Wdn")]:
+        off, cnt = mk.param_span(name)
+        a, b = g[off:off + cnt].astype(np.float64), gref[off:off + cnt].astype(np.float64)
+        l2 = np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30)
+        assert l2 <= 3e-2, (name, l2)
+    mk.close()
+
+
+def test_bf16_loss_curve_and_repeatability(ofa, oracle):
+    n = 12
+    ocfg, w0, tokens, starts, mk = small_bf16(ofa, oracle, nsteps=n)
+    ref = oracle.train(ocfg, w0, tokens, starts, n, precision="bf16_points")
+    mk.run(n)
+    losses = mk.losses().copy()
+    assert np.abs(losses - ref["losses"]).max() / ref["losses"].max() <= 1e-2
+    w_gpu = mk.read_weights()
+    off, cnt = mk.param_span("L1.Wup")
+    d_gpu = w_gpu[off:off + cnt] - oracle.flatten(ocfg, w0)[off:off + cnt]
+    d_ref = oracle.flatten(ocfg, ref["weights"])[off:off + cnt] - oracle.flatten(ocfg, w0)[off:off + cnt]
+    cos = float(np.dot(d_gpu, d_ref) / (np.linalg.norm(d_gpu) * np.linalg.norm(d_ref)))
+    assert cos >= 0.9                           # llm/b200/megakernel/compare_F.py: cosine of the weight delta
+    mk.close()
+    ocfg, w0, tokens, starts, mk2 = small_bf16(ofa, oracle, nsteps=n)
+    mk2.run(n)
+    np.testing.assert_array_equal(losses, mk2.losses())      # byte-identical loss file (check_loss.sh)
+    np.testing.assert_array_equal(w_gpu, mk2.read_weights())
+    mk2.close()
+
+
+def test_gpt_s_full_size_properties(ofa, oracle):
+    """BASELINE config 2 at full size: size-independent checks (the oracle would need minutes per step here)."""
+    cfg = ofa.default_config("gpt_s")
+    mk = ofa.Megakernel(cfg)
+    assert mk.num_params == 163007232 + 0 * 768
+    rng = np.random.default_rng(1234)
+    flat = (rng.standard_normal(mk.num_params, dtype=np.float32) * 0.02)
+    for name in ["gf"] + [f"L{l}.g{k}" for l in range(12) for k in (1, 2)]:
+        off, cnt = mk.param_span(name)
+        flat[off:off + cnt] = 1.0
+    sc = 1 / np.sqrt(24.0)
+    for l in range(12):
+        for t in ("Wo", "Wdn"):
+            off, cnt = mk.param_span(f"L{l}.{t}")
+            flat[off:off + cnt] *= sc
+    mk.load_weights(flat)
+    tokens = oracle.synthetic_tokens(50304, 1 << 20, 0)
+    mk.set_tokens(tokens)
+    mk.run(6)
+    losses = mk.losses()
+    assert abs(losses[0] - np.log(50304.0)) < 0.15           # random init: loss ~ ln V
+    assert np.all(np.isfinite(losses)) and losses[-1] < losses[0]
+    w = mk.read_weights()
+    assert np.all(np.isfinite(w)) and not np.array_equal(w, flat)
+    mk.close()
