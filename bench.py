@@ -1,0 +1,280 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: GPT-S (162M class, V=50304 untied, T=1024, B=4 => 4,096 tokens/step) trained by the
+persistent megakernel, with the live-weight decoder running concurrently on its own SM partition (116 train / 24 serve /
+8 reserved SMs). One "step" = one optimizer step. Prints ONE JSON line.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload split|train_only]
+
+Timing: W warm-up steps run in a first persistent launch; the K timed steps are ONE further persistent launch bracketed
+by CUDA events on the launching stream (and a barrier + synchronize on both sides), max over ranks. `value` counts the
+tokens all ranks trained on. The working set of a step (326 MB of bf16 weights + GBs of activations) exceeds the 126 MB L2,
+so no explicit flush is needed. `e2e` repeats the K steps through the public API with host buffers: token upload, launch,
+wait and loss read-back inside a host-timed region.
+
+--impl reference: the CPU implementation of the same step (the oracle port of the reference's PyTorch model) on all host
+cores, on a bounded sample (whole sequences of the same batch).
+"""
+import argparse
+import importlib
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+V, D, L, H, T, B = 50304, 768, 12, 12, 1024, 4
+TOKENS_PER_STEP = B * T
+P_MM = L * 12 * D * D + V * D                                   # matmul parameters
+FLOP_PER_STEP = 6 * TOKENS_PER_STEP * P_MM + L * 3.5 * (4 * B * H * T * T * (D // H) / 2)   # 3.307e12, causal attention counted once
+
+
+def measured_peaks():
+    try:
+        return json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))), "measured"
+    except Exception:
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks/throttle reasons sampled every 200 ms while the timed region runs."""
+    Q = "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, gpu_index):
+        self.gpu, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200", "-i", str(self.gpu)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.th = threading.Thread(target=self._read, daemon=True); self.th.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"], f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        # the load raises the clock: take the median of the upper half of the samples as "under load"
+        sm_sorted = sorted(sm)
+        under = sm_sorted[len(sm_sorted) // 2:] if sm_sorted else []
+        return {"sm_mhz": float(np.median(under)) if under else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def init_flat(mk, seed=1234):
+    """N(0, 0.02) weights with the reference's scaling (Wo/Wdown by 1/sqrt(2L), gammas 1), from numpy for speed."""
+    rng = np.random.default_rng(seed)
+    flat = rng.standard_normal(mk.num_params, dtype=np.float32) * np.float32(0.02)
+    sc = np.float32(1 / np.sqrt(2.0 * L))
+    for l in range(L):
+        for g in ("g1", "g2"):
+            off, cnt = mk.param_span(f"L{l}.{g}"); flat[off:off + cnt] = 1.0
+        for t in ("Wo", "Wdn"):
+            off, cnt = mk.param_span(f"L{l}.{t}"); flat[off:off + cnt] *= sc
+    off, cnt = mk.param_span("gf"); flat[off:off + cnt] = 1.0
+    return flat
+
+
+def cpu_step_tokens_per_s(max_seconds=30.0):
+    """The oracle's training step (fp32, all host threads) on whole sequences of the GPT-S batch; returns (tok/s, cores, sample)."""
+    import torch
+    from oracle import gpt_oracle as orc
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    cfg = orc.gpt_s_config()
+    w0 = orc.init_weights(cfg)
+    model = orc.GPTOracle(cfg, w0, "fp32")
+    opt = orc.make_optimizer(cfg, model)
+    tokens = orc.synthetic_tokens(V, 1 << 16, 0)
+    nseq, t_total, ntok = 0, 0.0, 0
+    # first sequence warms the allocator and is not counted; then as many sequences as fit in the time budget (at least one)
+    for i in range(1 + B):
+        seq = tokens[i * 1100:i * 1100 + T + 1].astype(np.int64)
+        x = torch.from_numpy(seq[None, :-1]).contiguous(); y = torch.from_numpy(seq[None, 1:]).contiguous()
+        t0 = time.perf_counter()
+        loss = model(x, y); loss.backward(); opt.step(); opt.zero_grad(set_to_none=True)
+        dt = time.perf_counter() - t0
+        if i == 0 and dt < max_seconds / 3:
+            continue
+        nseq += 1; t_total += dt; ntok += T
+        if t_total + dt > max_seconds:
+            break
+    return ntok / t_total, cores, f"{nseq} sequence(s) of {T} tokens, fp32 forward+backward+AdamW of the full 163M-parameter model, {t_total:.1f} s"
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    tps, cores, sample = cpu_step_tokens_per_s(max_seconds=25.0 * max(1, min(args.steps, 3)))
+    line = {"impl": "reference", "metric": "GPT-S 162M train tokens/s", "value": tps, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": TOKENS_PER_STEP / tps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "gpt_s V=50304 untied D=768 L=12 H=12 T=1024 B=4, CPU oracle port of the reference PyTorch model"},
+            "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="split", choices=["split", "train_only"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--phase-table", action="store_true", help="also print the per-phase busy table to stderr")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1")); local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        return run_reference(args, rank, world)
+
+    import torch
+    ofa = importlib.import_module("open-flapping-airplanes_b200")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the megakernel")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        ofa.dp.configure_nccl_env(8)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    W, K = max(3, args.warmup), args.steps
+    split = args.workload == "split"
+
+    cfg = ofa.default_config("gpt_s")
+    cfg.device = local_rank
+    cfg.data_seed = rank
+    if split:
+        cfg.infer_sms, cfg.reserved_sms, cfg.train_sms = 24, 8, 116
+        cfg.use_decode = 1 if rank == 0 else 0
+        if rank != 0:
+            cfg.reserved_sms = 32                      # other ranks leave the serving partition idle so that all ranks train on 116 SMs
+        prompt = np.random.default_rng(1234).integers(0, V, size=6)
+        for i, t in enumerate(prompt):
+            cfg.prompt[i] = int(t)
+        cfg.n_prompt, cfg.answer_len, cfg.temperature = 6, 256, 0.0
+        cfg.decode_out_cap = 1 << 20
+    elif world > 1:
+        cfg.reserved_sms = 8
+    dp = None
+    if world > 1:
+        cfg.dp_world, cfg.grad_bf16, cfg.ext_sync = world, 1, 1
+    mk = ofa.Megakernel(cfg)
+    mk.load_weights(init_flat(mk))
+    ntok = 1 << 22
+    tokens = np.random.default_rng(1000 + rank).integers(0, V, size=ntok, dtype=np.uint32)     # uniform ids, a distinct seed per rank
+    mk.set_tokens(tokens)
+    if world > 1:
+        dp = ofa.dp.DataParallel(mk, dist)               # NCCL gradient all-reduce ordered by device flags
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def run(n):
+        if dp is not None:
+            dp.enqueue(n)
+        mk.launch(n)
+        mk.wait(600000)
+        if dp is not None:
+            dp.finish()
+        return mk.last_launch_ms
+
+    run(W)
+    barrier()
+    dec0 = mk.decode_steps
+    sampler = ClockSampler(local_rank); sampler.start()
+    time.sleep(0.25)
+    ms = run(K)
+    barrier()
+    clocks = sampler.stop()
+    dec_steps = mk.decode_steps - dec0
+    if dist is not None:
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    losses = mk.losses()
+
+    # ---- end to end through the public API with host buffers (rank-local; inputs uploaded and results read inside the timed region)
+    window = tokens[: min(ntok, max(1 << 16, K * B * (T + 1) * 2))]
+    starts = np.random.default_rng(7).integers(0, window.size - T - 1, size=(K, B)).astype(np.uint32)
+    barrier()
+    t0 = time.perf_counter()
+    mk.set_tokens(window)
+    mk.set_starts(starts)
+    run(K)
+    e2e_losses = mk.losses()[-K:]
+    t1 = time.perf_counter()
+    e2e_s = t1 - t0
+    if dist is not None:
+        t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    assert np.all(np.isfinite(e2e_losses))
+
+    if rank == 0:
+        peaks, how = measured_peaks()
+        sms_used = cfg.train_sms if split else 148 - (cfg.reserved_sms if world > 1 else 0)
+        peak_tf = peaks["bf16_tflops_sustained"] * sms_used / 148.0
+        achieved_tf = FLOP_PER_STEP * K / (ms * 1e-3) / 1e12
+        value = world * TOKENS_PER_STEP * K / (ms * 1e-3)
+        # sampled decode tokens: of every 261 decode steps (5 forced + 256 sampled) 256 are counted, as the reference counts (ofa.cu:747-752)
+        dec_tok_s = (dec_steps * 256.0 / 261.0) / (ms * 1e-3) if split else None
+        line = {
+            "metric": "GPT-S 162M train tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": ("gpt_s V=50304 untied D=768 L=12 H=12 T=1024 B=4 (4096 tok/step/GPU), " +
+                                    ("116 train / 24 serve / 8 reserved SMs with concurrent batch-1 greedy decode (6-token prompt, 256 generated, repeating)" if split else "training only on all SMs")),
+                       "parallelism": f"dp{world}", "l2": "working set per step (>2 GB) exceeds the 126 MB L2; no flush needed",
+                       "projected_4000_steps_s": ms / K * 4000 / 1e3},
+            "decode_tok_s": dec_tok_s, "final_loss": float(losses[-1]), "first_loss": float(losses[0]),
+            "e2e": {"value": world * TOKENS_PER_STEP * K / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": int(window.nbytes / K + starts.nbytes / K), "d2h_bytes_per_step": 4},
+            "gpu_launches": 1,
+            "roofline": {"bound": "tensor", "achieved": achieved_tf, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved_tf / peak_tf,
+                         "traffic": None, "peak_source": f"{how} bf16_tflops_sustained x {sms_used}/148 SMs", "flop_per_step": FLOP_PER_STEP},
+            "clocks": clocks,
+        }
+        if args.phase_table:
+            tot = sum(p["busy_ns"] for p in mk.phases()) or 1
+            for p in sorted(mk.phases(), key=lambda p: -p["busy_ns"])[:40]:
+                print(f"  {p['name']:24s} tasks {p['ntasks']:6d}  busy {p['busy_ns'] / 1e6 / K:8.3f} ms/step  {100.0 * p['busy_ns'] / tot:5.1f} %", file=sys.stderr)
+        if world == 1 and not args.no_cpu_baseline:
+            tps, cores, sample = cpu_step_tokens_per_s(max_seconds=20.0)
+            line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}
+        print(json.dumps(line), flush=True)
+    mk.close()
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

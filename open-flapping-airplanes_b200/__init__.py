@@ -5,10 +5,11 @@ The directory name contains a hyphen, so import it with importlib.import_module(
 """
 from . import build as build_mod
 from . import capi
+from . import dp
 from .host import Megakernel, OfaError, default_config, flat_from_named, PARAM_ORDER_DOC
 from .tasks import DeviceBuffer, run_phases, gemm_phase, phase, bf16_round, to_bf16_bits, from_bf16_bits
 
 build = build_mod.build
 
-__all__ = ["build", "capi", "Megakernel", "OfaError", "default_config", "flat_from_named", "DeviceBuffer", "run_phases",
+__all__ = ["build", "capi", "dp", "Megakernel", "OfaError", "default_config", "flat_from_named", "DeviceBuffer", "run_phases",
            "gemm_phase", "phase", "bf16_round", "to_bf16_bits", "from_bf16_bits", "PARAM_ORDER_DOC"]

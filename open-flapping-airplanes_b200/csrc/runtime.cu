@@ -597,7 +597,7 @@ extern "C" int ofa_create(const ofa_config* cfg, ofa_ctx** out) {
     if (cfg->grad_bf16) return bail(OFA_BAD_CONFIG, "grad_bf16 needs the bf16 path");
   }
   if (cfg->use_decode && (cfg->n_prompt < 1 || cfg->n_prompt > 32)) return bail(OFA_BAD_CONFIG, "decode needs 1..32 prompt tokens");
-  if (cfg->use_decode && cfg->n_prompt + cfg->answer_len > m.T && cfg->answer_len > 0) return bail(OFA_BAD_CONFIG, "prompt + answer exceed ctx_len");
+  if (cfg->use_decode && cfg->n_prompt > m.T) return bail(OFA_BAD_CONFIG, "prompt longer than ctx_len");
   for (int i = 0; i < cfg->n_prompt && cfg->use_decode; i++) if (cfg->prompt[i] < 0 || cfg->prompt[i] >= m.V) return bail(OFA_BAD_CONFIG, "prompt token out of range");
   if (cfg->mode < 0 || cfg->mode > 3) return bail(OFA_BAD_CONFIG, "bad mode");
   if (cfg->mode == OFA_MODE_DECODE_ONLY && !cfg->use_decode) return bail(OFA_BAD_CONFIG, "decode-only mode needs use_decode");

@@ -177,7 +177,7 @@ def test_gpt_s_full_size_properties(ofa, oracle):
     mk.set_tokens(tokens)
     mk.run(6)
     losses = mk.losses()
-    assert abs(losses[0] - np.log(50304.0)) < 0.15           # random init: loss ~ ln V
+    assert 0.0 < losses[0] - np.log(50304.0) < 0.3          # random init: loss ~ ln V + var(logits)/2, logit std ~ 0.55
     assert np.all(np.isfinite(losses)) and losses[-1] < losses[0]
     w = mk.read_weights()
     assert np.all(np.isfinite(w)) and not np.array_equal(w, flat)
