@@ -155,6 +155,23 @@ int ofa_d2h(void* dst, const void* src, size_t bytes);
 int ofa_run_phases(int dtype, const ofa_dims* dims, const ofa_phase* phases, int nph, int repeats, const float* adam,
                    float* ms, ofa_status_t* status);
 
+/* ---- allocation-free entry point ------------------------------------------------------------------------------------
+ * No counterpart in the reference (its program allocates everything up front in main()). LayerNorm backward for the bf16
+ * path (d_model 768): dx = LN'(dy) [+ dres], dgamma (=|+=) column sums - the same arithmetic as the TK_LN_BWD + TK_LN_DG
+ * phases - as two ordinary kernel launches on `stream` (a cudaStream_t, or NULL) that call no cudaMalloc / cudaFree and no
+ * allocating library routine. It is for hosts that cannot allocate device memory on this path: processes whose GPU memory
+ * belongs to another allocator's pool, and loops that share the device with a resident persistent kernel, where the
+ * device-wide synchronisation of an allocation would stall that kernel. The dgamma partials live in a fixed device array
+ * (about 6 MB per GPU, kept until exit), so n_rows <= ofa_noalloc_max_rows() (32768); larger sizes return OFA_BAD_ARGUMENT
+ * and launch nothing. All pointers are device pointers supplied by the caller (bf16 for dx, dy, x, gamma, dres; dres may
+ * be NULL). The array is shared by every call and keeps the last call's partials (each call overwrites all it reads, so
+ * nothing needs clearing): calls that overlap on the GPU race and must be serialised by the caller. The first call on a
+ * device resolves the array's address with that device current; issue it before any stream capture begins. */
+int ofa_ln_bwd_noalloc(void* dx, float* dgamma, const void* dy, const void* x, const float* mean, const float* rstd,
+                       const void* gamma, const void* dres, int n_rows, int d_model, int accumulate, void* stream);
+int ofa_noalloc_max_rows(void);
+const char* ofa_noalloc_last_error(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -9,7 +9,7 @@ import subprocess
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(CSRC, "libofa_b200.so")
-SOURCES = ["runtime.cu"]
+SOURCES = ["runtime.cu", "noalloc.cu"]
 HEADERS = ["common.cuh", "task_api.h", "elementwise.cuh", "gemm_tc.cuh", "attn_mma.cuh", "simt_f32.cuh", "decode.cuh",
            "megakernel.cuh", os.path.join("..", "..", "include", "ofa_b200.h")]
 

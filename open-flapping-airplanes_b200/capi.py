@@ -80,6 +80,9 @@ PROTOTYPES = {
     "ofa_dev_free": (C.c_int, [C.c_void_p]),
     "ofa_h2d": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t]),
     "ofa_d2h": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t]),
+    "ofa_ln_bwd_noalloc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "ofa_noalloc_max_rows": (C.c_int, []),
+    "ofa_noalloc_last_error": (C.c_char_p, []),
     "ofa_run_phases": (C.c_int, [C.c_int, C.POINTER(Dims), C.POINTER(Phase), C.c_int, C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(Status)]),
 }
 
