@@ -1,0 +1,191 @@
+#!/usr/bin/env python
+"""Standalone kernel sweep on one B200 (BASELINE config 5): every task kind of the megakernel run alone as a one-kind job on
+the persistent scheduler, at the GPT-S shapes, timed with CUDA events and reported against the measured roofline.
+
+  python open-flapping-airplanes_b200/kernel_sweep.py [--only NAME[,NAME..]] [--repeats R] [--list]
+
+Each case rotates over enough independent buffer sets to exceed the 126 MB L2 between reuses (so DRAM numbers mean something),
+runs `repeats` passes over all sets in ONE launch, and prints one JSON line: time per pass, TFLOP/s or GB/s from the
+algorithmic work, and the fraction of the measured peak (MEASURED_PEAKS.json when present, else the pool's fallback figures).
+Inputs are N(0, 0.02) bf16 from a seeded generator. This is also the command the ncu captures under profiles/ were made with
+(`--only <case> --repeats 1`).
+"""
+import argparse
+import importlib
+import json
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+M = 4096
+D, FF, V, H, T, B = 768, 3072, 50304, 12, 1024, 4
+L2_BYTES = 126 << 20
+DIMS = dict(vocab=V, d_model=D, n_layer=1, n_head=H, ctx_len=T, batch=B)
+
+# name: (layout, epi, M, N, K)   layouts 0 NN, 1 NT, 2 TN; epilogues 0 store, 1 +res, 2 gelu, 3 dgelu, 4 f32
+GEMMS = {
+    "gemm_qkv": (0, 0, M, 3 * D, D), "gemm_proj": (0, 1, M, D, D), "gemm_up_gelu": (0, 2, M, FF, D), "gemm_down": (0, 1, M, D, FF),
+    "gemm_logits": (1, 0, M, V, D), "gemm_dpre_dgelu": (1, 3, M, FF, D), "gemm_dln2": (1, 0, M, D, FF), "gemm_dO": (1, 0, M, D, D),
+    "gemm_dln1": (1, 0, M, D, 3 * D), "gemm_head_dX": (0, 0, M, D, V), "gemm_dWqkv": (2, 4, D, 3 * D, M), "gemm_dWo": (2, 4, D, D, M),
+    "gemm_dWup": (2, 4, D, FF, M), "gemm_dWdown": (2, 4, FF, D, M), "gemm_head_dW": (2, 4, V, D, M),
+}
+OTHERS = ["attn_fwd", "attn_bwd", "adamw", "cross_entropy", "ln_fwd", "ln_bwd", "embed_bwd_wte", "decode_148sm", "decode_24sm"]
+
+
+def peaks():
+    try:
+        p = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))); return p["hbm_gbs"], p["bf16_tflops"], "measured"
+    except Exception:
+        return 6650.0, 1590.0, "fallback"
+
+
+def rand_bf16(ofa, rng, shape, scale=0.02):
+    return ofa.DeviceBuffer.from_host(rng.standard_normal(shape, dtype=np.float32) * scale, "bf16")
+
+
+def run_gemm(ofa, name, repeats, nsub):
+    K = ofa.capi
+    layout, epi, Mm, Nn, Kk = GEMMS[name]
+    rng = np.random.default_rng(0)
+    ashape = (Mm, Kk) if layout != 2 else (Kk, Mm)
+    bshape = (Kk, Nn) if layout != 1 else (Nn, Kk)
+    out_b = 4 if epi == 4 else 2
+    bytes_set = 2 * (Mm * Kk + Kk * Nn) + out_b * Mm * Nn + (2 * Mm * Nn if epi in (1, 2, 3) else 0)
+    nsets = max(1, min(16, -(-2 * L2_BYTES // bytes_set)))
+    keep, phases = [], []
+    for _ in range(nsets):
+        A = rand_bf16(ofa, rng, ashape); Bm = rand_bf16(ofa, rng, bshape)
+        C = ofa.DeviceBuffer((Mm, Nn), np.float32 if epi == 4 else "bf16")
+        aux = rand_bf16(ofa, rng, (Mm, Nn), 1.0) if epi in (1, 3) else (ofa.DeviceBuffer((Mm, Nn), "bf16") if epi == 2 else None)
+        keep += [A, Bm, C, aux]
+        phases.append(ofa.gemm_phase(layout, epi, Mm, Nn, Kk, A, ashape[1], Bm, bshape[1], C, Nn, aux, Nn if aux is not None else 0, nsub=nsub))
+    ms = ofa.run_phases(K.DTYPE_BF16, DIMS, phases, repeats=repeats) / (repeats * nsets)
+    flop = 2.0 * Mm * Nn * Kk
+    return {"kernel": name, "shape": [Mm, Nn, Kk], "ms": ms, "tflops": flop / ms / 1e9, "bound": "tensor", "algorithmic_bytes": bytes_set, "buffer_sets": nsets}
+
+
+def run_attn(ofa, which, repeats):
+    K = ofa.capi
+    rng = np.random.default_rng(1)
+    N = B * T
+    nsets = 6
+    keep, phases = [], []
+    for _ in range(nsets):
+        qkv = rand_bf16(ofa, rng, (N, 3 * D), 1.0); dO = rand_bf16(ofa, rng, (N, D), 1.0)
+        o = ofa.DeviceBuffer((N, D), "bf16"); lse = ofa.DeviceBuffer((B, H, T), np.float32); Dr = ofa.DeviceBuffer((B, H, T), np.float32); dqkv = ofa.DeviceBuffer((N, 3 * D), "bf16")
+        keep += [qkv, dO, o, lse, Dr, dqkv]
+        if which == "attn_fwd":
+            phases.append(ofa.phase(K.TK_ATT_FWD, [qkv, o, lse]))
+        else:
+            ofa.run_phases(K.DTYPE_BF16, DIMS, [ofa.phase(K.TK_ATT_FWD, [qkv, o, lse])])
+            phases += [ofa.phase(K.TK_ATT_PREP, [o, dO, Dr]), ofa.phase(K.TK_ATT_BWD, [qkv, dO, lse, Dr, dqkv, o])]
+    ms = ofa.run_phases(K.DTYPE_BF16, DIMS, phases, repeats=repeats) / (repeats * nsets)
+    fwd_flop = 4.0 * B * H * T * T * 64 / 2
+    flop = fwd_flop if which == "attn_fwd" else 2.5 * fwd_flop
+    return {"kernel": which, "shape": [B, H, T, 64], "ms": ms, "tflops": flop / ms / 1e9, "bound": "tensor", "buffer_sets": nsets}
+
+
+def run_adamw(ofa, repeats):
+    K = ofa.capi
+    n = 163007232
+    rng = np.random.default_rng(2)
+    W = ofa.DeviceBuffer.from_host(rng.standard_normal(n, dtype=np.float32) * 0.02); G = ofa.DeviceBuffer.from_host(rng.standard_normal(n, dtype=np.float32) * 0.01)
+    Mb = ofa.DeviceBuffer((n,), np.float32); Vb = ofa.DeviceBuffer((n,), np.float32); Wa = ofa.DeviceBuffer((n,), "bf16"); nd = ofa.DeviceBuffer.from_host(np.array([[0, 768]], np.int32))
+    ms = ofa.run_phases(K.DTYPE_BF16, DIMS, [ofa.phase(K.TK_ADAMW, [W, G, Mb, Vb, Wa, nd], n=n, i0=1)], repeats=repeats, adam=[6e-4, 0.9, 0.95, 1e-8, 0.1, 1.0]) / repeats
+    by = 30.0 * n
+    return {"kernel": "adamw", "shape": [n], "ms": ms, "gbs": by / ms / 1e6, "bound": "hbm", "algorithmic_bytes": by, "bytes_per_param": 30}
+
+
+def run_ce(ofa, repeats):
+    K = ofa.capi
+    rng = np.random.default_rng(3)
+    N = B * T
+    lg = ofa.DeviceBuffer.from_host(rng.standard_normal((N, V), dtype=np.float32) * 0.5, "bf16")
+    tg = ofa.DeviceBuffer.from_host(rng.integers(0, V, N).astype(np.int32)); loss = ofa.DeviceBuffer((N,), np.float32)
+    ms = ofa.run_phases(K.DTYPE_BF16, DIMS, [ofa.phase(K.TK_CE, [lg, tg, loss])], repeats=repeats) / repeats
+    by = 2.0 * N * V * 2
+    return {"kernel": "cross_entropy", "shape": [N, V], "ms": ms, "gbs": by / ms / 1e6, "bound": "hbm", "algorithmic_bytes": by}
+
+
+def run_ln(ofa, which, repeats):
+    K = ofa.capi
+    rng = np.random.default_rng(4)
+    N = B * T
+    nsets = 24
+    keep, phases = [], []
+    gamma = rand_bf16(ofa, rng, (D,), 1.0)
+    for _ in range(nsets):
+        x = rand_bf16(ofa, rng, (N, D), 1.0); y = ofa.DeviceBuffer((N, D), "bf16"); mean = ofa.DeviceBuffer((N,), np.float32); rstd = ofa.DeviceBuffer((N,), np.float32)
+        keep += [x, y, mean, rstd]
+        if which == "ln_fwd":
+            phases.append(ofa.phase(K.TK_LN_FWD, [y, mean, rstd, x, gamma]))
+        else:
+            dy = rand_bf16(ofa, rng, (N, D), 1.0); dx = ofa.DeviceBuffer((N, D), "bf16"); part = ofa.DeviceBuffer((N // 16, D), np.float32)
+            keep += [dy, dx, part]
+            ofa.run_phases(K.DTYPE_BF16, DIMS, [ofa.phase(K.TK_LN_FWD, [y, mean, rstd, x, gamma])])
+            phases.append(ofa.phase(K.TK_LN_BWD, [dx, part, dy, x, mean, rstd, gamma, None]))
+    ms = ofa.run_phases(K.DTYPE_BF16, DIMS, phases, repeats=repeats) / (repeats * nsets)
+    by = (2.0 if which == "ln_fwd" else 3.0) * N * D * 2
+    return {"kernel": which, "shape": [N, D], "ms": ms, "gbs": by / ms / 1e6, "bound": "hbm", "algorithmic_bytes": by, "buffer_sets": nsets}
+
+
+def run_embed_bwd(ofa, repeats):
+    K = ofa.capi
+    rng = np.random.default_rng(5)
+    N = B * T
+    tok = ofa.DeviceBuffer.from_host(rng.integers(0, V, N).astype(np.int32)); dx = rand_bf16(ofa, rng, (N, D), 1.0); dw = ofa.DeviceBuffer((V, D), np.float32)
+    ms = ofa.run_phases(K.DTYPE_BF16, DIMS, [ofa.phase(K.TK_EMB_WTE, [dw, dx, tok])], repeats=repeats) / repeats
+    by = V * D * 4.0 + N * D * 2.0
+    return {"kernel": "embed_bwd_wte", "shape": [V, D, N], "ms": ms, "gbs": by / ms / 1e6, "bound": "hbm", "algorithmic_bytes": by}
+
+
+def run_decode(ofa, sms, ntok):
+    cfg = ofa.default_config("gpt_s")
+    cfg.mode, cfg.use_decode, cfg.infer_sms, cfg.reserved_sms = ofa.capi.MODE_DECODE_ONLY, 1, sms, 0
+    for i, t in enumerate(np.random.default_rng(1234).integers(0, V, 6)):
+        cfg.prompt[i] = int(t)
+    cfg.n_prompt, cfg.answer_len = 6, 256
+    mk = ofa.Megakernel(cfg)
+    rng = np.random.default_rng(6)
+    mk.load_weights(rng.standard_normal(mk.num_params, dtype=np.float32) * np.float32(0.02))
+    mk.run(64)
+    ms = mk.run(ntok)
+    mk.close()
+    by = 2.0 * (12 * 12 * D * D + V * D) + 36864.0 * 131      # weights + KV at the mean position of a 261-step answer cycle
+    return {"kernel": f"decode_{sms}sm", "shape": [sms], "ms": ms / ntok, "tok_s": ntok / ms * 1e3, "gbs": by / (ms / ntok) / 1e6, "bound": "hbm", "algorithmic_bytes": by}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default="")
+    ap.add_argument("--repeats", type=int, default=5)
+    ap.add_argument("--nsub", type=int, default=0)
+    ap.add_argument("--list", action="store_true")
+    a = ap.parse_args()
+    names = list(GEMMS) + OTHERS
+    if a.list:
+        print("\n".join(names)); return
+    sel = [n for n in a.only.split(",") if n] or names
+    ofa = importlib.import_module("open-flapping-airplanes_b200")
+    hbm, tf, how = peaks()
+    for n in sel:
+        if n in GEMMS: r = run_gemm(ofa, n, a.repeats, a.nsub)
+        elif n in ("attn_fwd", "attn_bwd"): r = run_attn(ofa, n, a.repeats)
+        elif n == "adamw": r = run_adamw(ofa, a.repeats)
+        elif n == "cross_entropy": r = run_ce(ofa, a.repeats)
+        elif n in ("ln_fwd", "ln_bwd"): r = run_ln(ofa, n, a.repeats)
+        elif n == "embed_bwd_wte": r = run_embed_bwd(ofa, a.repeats)
+        elif n == "decode_148sm": r = run_decode(ofa, 148, 261 * max(1, a.repeats))
+        elif n == "decode_24sm": r = run_decode(ofa, 24, 261 * max(1, a.repeats))
+        else: raise SystemExit(f"unknown case {n}")
+        r["frac"] = (r["tflops"] / tf) if r["bound"] == "tensor" else (r["gbs"] / hbm)
+        r["peak"] = f"{how}: {tf if r['bound'] == 'tensor' else hbm} {'TFLOP/s (burst)' if r['bound'] == 'tensor' else 'GB/s'}"
+        print(json.dumps(r), flush=True)
+
+
+if __name__ == "__main__":
+    main()
