@@ -63,7 +63,7 @@ typedef struct {
   int bucket_bytes;         /* target bucket size for ext_sync (0 = 25 MiB)                                       */
   int gemm_nsub;            /* consecutive 128-wide N tiles per GEMM task (0 = default)                           */
   double timeout_s;         /* device-side bound for any dependency wait (0 = default 20 s)                       */
-  int device;               /* CUDA device ordinal                                                                 */
+  int device;               /* CUDA device ordinal; < 0 = planning context: layout, buckets and phase graphs are built and can be queried, nothing touches a device and nothing can be launched */
 } ofa_config;
 
 /* preset: "tiny" (BASELINE config 1) or "gpt_s" (config 2). */
@@ -108,6 +108,8 @@ int ofa_read_losses(ofa_ctx* ctx, float* out, size_t n);                  /* los
 int ofa_read_step_times(ofa_ctx* ctx, unsigned long long* out, size_t n); /* %globaltimer ns at the end of each step of the last launch */
 int ofa_num_phases(const ofa_ctx* ctx);
 int ofa_phase_info(const ofa_ctx* ctx, int phase, char* name, size_t name_cap, int* kind, int* ntasks, unsigned long long* busy_ns);
+/* dependencies of a phase: job 0 = training graph, 1 = serving graph; returns their number and fills up to cap (phase, step-delta) pairs (Job::deps, ofa.cu:103-105) */
+int ofa_phase_deps(const ofa_ctx* ctx, int job, int phase, int* dep_phase, int* dep_delta, int cap);
 int ofa_decode_steps(const ofa_ctx* ctx);                                  /* tokens processed by the serving job      */
 int ofa_read_decode_tokens(ofa_ctx* ctx, int* out, size_t cap);            /* the pinned ring: sampled ids, OFA_OUT_* markers, -1 = unused */
 int ofa_read_decode_logits(ofa_ctx* ctx, float* out, size_t n);            /* fp32 logits of the last decoded token    */

@@ -82,14 +82,18 @@ bool encode_map(CUtensorMap* m, const void* base, uint64_t inner, uint64_t outer
 struct Arena {   // device allocations owned by one context / one ofa_run_phases call
   std::vector<void*> ptrs;
   bool ok = true;
+  bool dry = false;            // planning mode (no device): hands out distinct, aligned, never-dereferenced addresses
+  uintptr_t bump = 0x100000000ull;
   template <class T> T* alloc(size_t n, bool zero = true) {
     void* p = nullptr;
     if (n == 0) n = 1;
+    if (dry) { p = reinterpret_cast<void*>(bump); bump += (n * sizeof(T) + 1023) / 1024 * 1024; return reinterpret_cast<T*>(p); }
     if (cudaMalloc(&p, n * sizeof(T)) != cudaSuccess) { ok = false; return nullptr; }
     if (zero) cudaMemset(p, 0, n * sizeof(T));
     ptrs.push_back(p);
     return reinterpret_cast<T*>(p);
   }
+  void h2d(void* dst, const void* src, size_t bytes) { if (!dry) cudaMemcpy(dst, src, bytes, cudaMemcpyHostToDevice); }
   void free_all() { for (void* p : ptrs) cudaFree(p); ptrs.clear(); }
 };
 
@@ -110,6 +114,7 @@ bool prepare_gemm_bf16(PhaseDesc& d, Arena& ar, int nsub_cfg, int nblocks, std::
   g.nsub = nsub;
   d.tiles_m = tm;
   d.ntasks = tm * ((tn + nsub - 1) / nsub);
+  if (ar.dry) { g.tmA = ar.alloc<CUtensorMap>(2, false); g.tmB = reinterpret_cast<const CUtensorMap*>(g.tmA) + 1; return true; }
   CUtensorMap hm[2];
   const bool a_kmajor = d.layout != GL_TN, b_kmajor = d.layout == GL_NT;
   bool ok = a_kmajor ? encode_map(&hm[0], g.A, g.K, g.M, g.lda, 64, 128) : encode_map(&hm[0], g.A, g.M, g.K, g.lda, 64, 64);
@@ -206,6 +211,7 @@ struct ofa_ctx {
   int* d_ext_ready = nullptr; int* d_ext_done = nullptr;   // device flags [32] each: gradients of bucket b ready / all-reduce of bucket b done
   std::vector<Span> buckets;
   cudaStream_t stream = nullptr; cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  bool dry = false;
   bool in_flight = false; int steps_total = 0, last_nsteps = 0; float last_ms = 0.f; int dec_steps_total = 0;
   std::string err;
 };
@@ -426,7 +432,7 @@ bool build_train_graph(ofa_ctx* c) {
         d.n = n; d.i0 = (int)nodecay.size(); d.i1 = gbf ? 1 : 0;
         std::vector<int2> nd; for (const Span& sp : nodecay) nd.push_back(make_int2((int)(sp.off - off), (int)(sp.off - off + sp.n)));
         int2* dn = c->ar.alloc<int2>(std::max<size_t>(1, nd.size()));
-        if (dn && !nd.empty()) cudaMemcpy(dn, nd.data(), nd.size() * sizeof(int2), cudaMemcpyHostToDevice);
+        if (dn && !nd.empty()) c->ar.h2d(dn, nd.data(), nd.size() * sizeof(int2));
         d.p[5] = dn;
         return d;
       };
@@ -470,7 +476,7 @@ bool build_decode_graph(ofa_ctx* c) {
   dp.wte = Wact + lay.wte; dp.wpe = Wact + lay.wpe; dp.head = Wact + lay.head; dp.gf = Wact + lay.gf;
   std::vector<const void*> hq(L), ho(L), hu(L), hd(L), h1(L), h2(L);
   for (int l = 0; l < L; l++) { hq[l] = Wact + lay.wqkv[l]; ho[l] = Wact + lay.wo[l]; hu[l] = Wact + lay.wup[l]; hd[l] = Wact + lay.wdn[l]; h1[l] = Wact + lay.g1[l]; h2[l] = Wact + lay.g2[l]; }
-  auto up = [&](const std::vector<const void*>& h) { const void** d = c->ar.alloc<const void*>(L); if (d) cudaMemcpy(d, h.data(), L * sizeof(void*), cudaMemcpyHostToDevice); return (const void* const*)d; };
+  auto up = [&](const std::vector<const void*>& h) { const void** d = c->ar.alloc<const void*>(L); if (d) c->ar.h2d(d, h.data(), L * sizeof(void*)); return (const void* const*)d; };
   dp.wqkv = up(hq); dp.wo = up(ho); dp.wup = up(hu); dp.wdn = up(hd); dp.g1 = up(h1); dp.g2 = up(h2);
   DecodeState& st = dp.st;
   st.xw = c->ar.alloc<unsigned long long>(D); st.xr = c->ar.alloc<unsigned long long>(D);
@@ -480,17 +486,20 @@ bool build_decode_graph(ofa_ctx* c) {
   st.kv = c->ar.alloc<T>((size_t)L * 2 * m.H * m.T * m.DH);
   st.logits = c->ar.alloc<float>(m.V);
   c->out_cap = cfg.decode_out_cap > 0 ? cfg.decode_out_cap : 65536;
-  if (cudaHostAlloc(&c->h_out, sizeof(int) * c->out_cap, cudaHostAllocMapped) != cudaSuccess) { c->err = "cudaHostAlloc failed"; return false; }
-  memset(c->h_out, 0xFF, sizeof(int) * c->out_cap);
-  cudaHostGetDevicePointer(&c->d_out, c->h_out, 0);
+  if (c->ar.dry) { c->d_out = c->ar.alloc<int>(c->out_cap); }
+  else {
+    if (cudaHostAlloc(&c->h_out, sizeof(int) * c->out_cap, cudaHostAllocMapped) != cudaSuccess) { c->err = "cudaHostAlloc failed"; return false; }
+    memset(c->h_out, 0xFF, sizeof(int) * c->out_cap);
+    cudaHostGetDevicePointer(&c->d_out, c->h_out, 0);
+  }
   st.out_tokens = c->d_out; st.out_cap = c->out_cap;
   c->d_forced = c->ar.alloc<int>(std::max(1, cfg.n_prompt));
   if (!c->ar.ok) { c->err = "out of device memory (decode state)"; return false; }
-  cudaMemcpy(c->d_forced, cfg.prompt, sizeof(int) * cfg.n_prompt, cudaMemcpyHostToDevice);
+  c->ar.h2d(c->d_forced, cfg.prompt, sizeof(int) * cfg.n_prompt);
   dp.forced = c->d_forced; dp.nforced = cfg.n_prompt; dp.answer_len = cfg.answer_len; dp.auto_reset = 1;
   dp.temperature = cfg.temperature; dp.seed = cfg.decode_seed;
   int scal[8] = {cfg.prompt[0], 0, 0, 0, 0, 0, 0, 0};
-  cudaMemcpy(c->d_scal, scal, sizeof scal, cudaMemcpyHostToDevice);
+  c->ar.h2d(c->d_scal, scal, sizeof scal);
 
   std::vector<HostPhase>& P = c->dec_ph; P.clear();
   auto mk = [&](const std::string& name, int kind, int ntasks, int layer) {
@@ -532,6 +541,7 @@ bool probe_smids(ofa_ctx* c) {
 }
 
 int read_f32(ofa_ctx* c, const float* src, float* out, size_t n) {
+  if (c && c->dry) return fail(c, OFA_BAD_ARGUMENT, "planning context (device < 0) has no device memory");
   if (!c || !out || n > c->lay.total) return fail(c, OFA_BAD_ARGUMENT, "bad size");
   if (c->in_flight) return fail(c, OFA_BAD_ARGUMENT, "launch in flight: call ofa_wait first");
   return cudaMemcpy(out, src, n * sizeof(float), cudaMemcpyDeviceToHost) == cudaSuccess ? OFA_OK : fail(c, OFA_CUDA_ERROR, cudaGetErrorString(cudaGetLastError()));
@@ -565,6 +575,7 @@ extern "C" const char* ofa_last_error(const ofa_ctx* ctx) { return ctx ? ctx->er
 
 extern "C" void ofa_destroy(ofa_ctx* c) {
   if (!c) return;
+  if (c->dry) { delete c; return; }
   cudaSetDevice(c->device);
   if (c->in_flight) cudaStreamSynchronize(c->stream);
   c->train_job.free_all(); c->dec_job.free_all();
@@ -604,15 +615,22 @@ extern "C" int ofa_create(const ofa_config* cfg, ofa_ctx** out) {
   if (cfg->dp_world < 1) return bail(OFA_BAD_CONFIG, "dp_world < 1");
 
   c->device = cfg->device;
-  if (cudaSetDevice(c->device) != cudaSuccess) return bail(OFA_CUDA_ERROR, "cudaSetDevice failed (no CUDA device?)");
-  cudaDeviceProp prop;
-  if (cudaGetDeviceProperties(&prop, c->device) != cudaSuccess) return bail(OFA_CUDA_ERROR, "cudaGetDeviceProperties failed");
-  if (prop.major != 10) return bail(OFA_CUDA_ERROR, "this library contains sm_100a code only; device is sm_" + std::to_string(prop.major * 10 + prop.minor));
-  c->num_sms = prop.multiProcessorCount;
+  const bool dry = cfg->device < 0;      // planning mode: build layout, buckets and phase graphs without touching a device
+  c->ar.dry = dry; c->dry = dry;
+  if (dry) { c->num_sms = 148; }
+  else {
+    if (cudaSetDevice(c->device) != cudaSuccess) return bail(OFA_CUDA_ERROR, "cudaSetDevice failed (no CUDA device?)");
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, c->device) != cudaSuccess) return bail(OFA_CUDA_ERROR, "cudaGetDeviceProperties failed");
+    if (prop.major != 10) return bail(OFA_CUDA_ERROR, "this library contains sm_100a code only; device is sm_" + std::to_string(prop.major * 10 + prop.minor));
+    c->num_sms = prop.multiProcessorCount;
+  }
   c->nblocks = 2 * c->num_sms;
   c->smem = smem_for(c->bf, m.T, m.N);
-  if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess) return bail(OFA_CUDA_ERROR, "stream");
-  cudaEventCreate(&c->ev0); cudaEventCreate(&c->ev1);
+  if (!dry) {
+    if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess) return bail(OFA_CUDA_ERROR, "stream");
+    cudaEventCreate(&c->ev0); cudaEventCreate(&c->ev1);
+  }
   // SM split
   int infer = cfg->use_decode ? std::max(0, cfg->infer_sms) : 0, resv = std::max(0, cfg->reserved_sms);
   if (cfg->use_decode && infer == 0) infer = c->num_sms >= 148 ? 24 : std::max(1, c->num_sms / 6);
@@ -629,11 +647,13 @@ extern "C" int ofa_create(const ofa_config* cfg, ofa_ctx** out) {
   if (cfg->grad_bf16) c->Gbf = c->ar.alloc<bf16>(NP); else c->G32 = c->ar.alloc<float>(NP);
   c->d_status = c->ar.alloc<DevStatus>(1); c->d_finished = c->ar.alloc<int>(1); c->d_t_end = c->ar.alloc<unsigned long long>(1);
   if (!c->ar.ok) return bail(OFA_CUDA_ERROR, "out of device memory (parameters)");
-  if (cudaHostAlloc(&c->h_live, sizeof(Live), cudaHostAllocMapped) != cudaSuccess) return bail(OFA_CUDA_ERROR, "cudaHostAlloc failed");
-  memset(c->h_live, 0, sizeof(Live)); cudaHostGetDevicePointer(&c->d_live, c->h_live, 0);
+  if (!dry) {
+    if (cudaHostAlloc(&c->h_live, sizeof(Live), cudaHostAllocMapped) != cudaSuccess) return bail(OFA_CUDA_ERROR, "cudaHostAlloc failed");
+    memset(c->h_live, 0, sizeof(Live)); cudaHostGetDevicePointer(&c->d_live, c->h_live, 0);
+  }
   c->d_ext_ready = c->ar.alloc<int>(64); c->d_ext_done = c->d_ext_ready ? c->d_ext_ready + 32 : nullptr;
   if (!c->ar.ok) return bail(OFA_CUDA_ERROR, "out of device memory");
-  if (!probe_smids(c)) return bail(OFA_CUDA_ERROR, std::string("SM probe launch failed: ") + cudaGetErrorString(cudaGetLastError()));
+  if (!dry && !probe_smids(c)) return bail(OFA_CUDA_ERROR, std::string("SM probe launch failed: ") + cudaGetErrorString(cudaGetLastError()));
 
   Ctx& C = c->C;
   memset(&C, 0, sizeof C);
@@ -671,6 +691,7 @@ extern "C" int ofa_param_span(const ofa_ctx* c, const char* name, size_t* offset
 }
 
 extern "C" int ofa_load_weights(ofa_ctx* c, const float* flat, size_t n) {
+  if (c && c->dry) return fail(c, OFA_BAD_ARGUMENT, "planning context (device < 0) has no device memory");
   if (!c || !flat || n != c->lay.total) return fail(c, OFA_BAD_ARGUMENT, "weight count does not match the layout");
   if (c->in_flight) return fail(c, OFA_BAD_ARGUMENT, "launch in flight");
   cudaSetDevice(c->device);
@@ -714,6 +735,7 @@ extern "C" int ofa_load_adam_state(ofa_ctx* c, const float* mm, const float* vv,
 }
 
 extern "C" int ofa_set_tokens(ofa_ctx* c, const uint32_t* tokens, size_t n) {
+  if (c && c->dry) return fail(c, OFA_BAD_ARGUMENT, "planning context (device < 0) has no device memory");
   if (!c || !tokens || n < (size_t)c->md.T + 2) return fail(c, OFA_BAD_ARGUMENT, "need more than ctx_len + 1 tokens");
   if (c->in_flight) return fail(c, OFA_BAD_ARGUMENT, "launch in flight");
   for (size_t i = 0; i < n; i++) if (tokens[i] >= (uint32_t)c->md.V) return fail(c, OFA_BAD_ARGUMENT, "token id out of range");
@@ -736,6 +758,7 @@ extern "C" int ofa_set_starts(ofa_ctx* c, const uint32_t* starts, size_t nsteps)
 }
 
 extern "C" int ofa_launch(ofa_ctx* c, int nsteps) {
+  if (c && c->dry) return fail(c, OFA_BAD_ARGUMENT, "planning context (device < 0) cannot launch");
   if (!c || nsteps <= 0) return fail(c, OFA_BAD_ARGUMENT, "nsteps must be positive");
   if (c->in_flight) return fail(c, OFA_BAD_ARGUMENT, "previous launch still in flight: call ofa_wait");
   const bool train_on = c->C.train_sms > 0;
@@ -836,8 +859,16 @@ extern "C" int ofa_phase_info(const ofa_ctx* c, int phase, char* name, size_t na
   if (name && name_cap) { strncpy(name, p.name.c_str(), name_cap - 1); name[name_cap - 1] = 0; }
   if (kind) *kind = p.d.kind;
   if (ntasks) *ntasks = p.d.ntasks;
-  if (busy_ns) { cudaSetDevice(c->device); cudaMemcpy(busy_ns, c->d_phase_busy + phase, 8, cudaMemcpyDeviceToHost); }
+  if (busy_ns) { if (c->dry) *busy_ns = 0; else { cudaSetDevice(c->device); cudaMemcpy(busy_ns, c->d_phase_busy + phase, 8, cudaMemcpyDeviceToHost); } }
   return OFA_OK;
+}
+extern "C" int ofa_phase_deps(const ofa_ctx* c, int job, int phase, int* dep_phase, int* dep_delta, int cap) {
+  if (!c || (job != 0 && job != 1)) return -1;
+  const std::vector<HostPhase>& P = job == 0 ? c->train_ph : c->dec_ph;
+  if (phase < 0 || phase >= (int)P.size()) return -1;
+  const int n = (int)P[phase].deps.size();
+  for (int i = 0; i < n && i < cap; i++) { if (dep_phase) dep_phase[i] = P[phase].deps[i].phase; if (dep_delta) dep_delta[i] = P[phase].deps[i].delta; }
+  return n;
 }
 extern "C" int ofa_decode_steps(const ofa_ctx* c) { return c ? c->dec_steps_total : 0; }
 extern "C" int ofa_read_decode_tokens(ofa_ctx* c, int* out, size_t cap) {

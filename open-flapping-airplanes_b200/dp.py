@@ -27,6 +27,26 @@ def bucket_schedule(buckets, nsteps):
     return [(s, b) for s in range(nsteps) for b in range(len(buckets))]
 
 
+def allreduce_buckets_host(dist, flat, buckets, nsteps=1):
+    """The communication the device-flag schedule performs, without the flags: sum-all-reduce every bucket of `flat` in
+    place, in schedule order. Works on CPU tensors over gloo (used by the CPU tests) and defines what the GPU path must equal."""
+    for _, b in bucket_schedule(buckets, nsteps):
+        off, cnt = buckets[b]
+        dist.all_reduce(flat[off:off + cnt])
+    return flat
+
+
+def buckets_partition_params(buckets, num_params):
+    """True when the buckets are disjoint and cover [0, num_params) exactly."""
+    spans = sorted(buckets)
+    pos = 0
+    for off, cnt in spans:
+        if off != pos or cnt <= 0:
+            return False
+        pos = off + cnt
+    return pos == num_params
+
+
 class _DevArray:
     """Minimal __cuda_array_interface__ wrapper so torch can view library-owned device memory without a copy."""
 

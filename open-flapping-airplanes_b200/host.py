@@ -148,6 +148,13 @@ class Megakernel:
             res.append({"name": name.value.decode(), "kind": kind.value, "ntasks": nt.value, "busy_ns": busy.value})
         return res
 
+    def phase_deps(self, phase, job=0):
+        ph = (C.c_int * 64)(); de = (C.c_int * 64)()
+        n = self.lib.ofa_phase_deps(self.h, job, phase, ph, de, 64)
+        if n < 0:
+            raise OfaError(capi.BAD_ARGUMENT, "no such phase")
+        return [(ph[i], de[i]) for i in range(min(n, 64))]
+
     # ---- decode
     @property
     def decode_steps(self):

@@ -1,0 +1,105 @@
+"""Host logic without a GPU: planning contexts (device < 0) build the flat layout, the gradient buckets and the training /
+serving phase graphs exactly as a real context does; these tests check their structure."""
+import numpy as np
+import pytest
+
+
+def plan(ofa, preset, **kw):
+    cfg = ofa.default_config(preset)
+    cfg.device = -1
+    for k, v in kw.items():
+        setattr(cfg, k, v)
+    return ofa.Megakernel(cfg)
+
+
+@pytest.mark.parametrize("preset,kw", [("gpt_s", {}), ("gpt_s", dict(tied_head=1)), ("gpt_s", dict(mode=1)), ("gpt_s", dict(mode=2)),
+                                       ("gpt_s", dict(dp_world=8, grad_bf16=1, ext_sync=1)), ("tiny", {}), ("tiny", dict(tied_head=1)), ("tiny", dict(mode=2))])
+def test_training_graph_is_topologically_ordered(ofa, preset, kw):
+    mk = plan(ofa, preset, **kw)
+    ph = mk.phases()
+    names = [p["name"] for p in ph]
+    assert len(set(names)) == len(names) and names[0] == "data" and names[-1] == "step barrier"
+    reached_from_prev_step = 0
+    for i, p in enumerate(ph):
+        assert p["ntasks"] > 0
+        deps = mk.phase_deps(i)
+        for d, delta in deps:
+            assert 0 <= d < len(ph) and delta in (0, -1)
+            if delta == 0:
+                assert d < i, f"{p['name']} depends on later phase {names[d]} of the same step"   # => every dependency is a lower ticket
+            else:
+                reached_from_prev_step += 1
+        if i > 0 and p["name"] != "data":
+            assert any(delta == 0 for _, delta in deps), f"{p['name']} has no producer in its own step"
+    assert reached_from_prev_step >= 1                     # steps are chained
+    mode = kw.get("mode", 0)
+    if mode == 0:
+        L = mk.cfg.n_layer
+        for l in range(L):                                 # next step's forward of layer l waits for this step's AdamW of layer l
+            i = names.index(f"L{l} ln1")
+            assert (names.index(f"adamw L{l}"), -1) in mk.phase_deps(i)
+        head = "adamw wte" if kw.get("tied_head") else "adamw head"
+        assert (names.index(head), -1) in mk.phase_deps(names.index("logits"))
+        assert (names.index("head dW"), -1) in mk.phase_deps(names.index("lnf"))
+        seen, todo = set(), [names.index(head)]            # same-step ancestors of the head's AdamW (direct, or through an all-reduce gate)
+        while todo:
+            for d, delta in mk.phase_deps(todo.pop()):
+                if delta == 0 and d not in seen:
+                    seen.add(d); todo.append(d)
+        assert names.index("head dX") in seen              # the head may not be updated while dX still reads it
+    mk.close()
+
+
+def test_gpt_s_task_counts_and_layout(ofa):
+    mk = plan(ofa, "gpt_s")
+    assert mk.num_params == 163007232
+    ph = {p["name"]: p for p in mk.phases()}
+    assert ph["embed"]["ntasks"] == 256 and ph["L0 ln1"]["ntasks"] == 256 and ph["cross-entropy"]["ntasks"] == 1024
+    assert ph["L3 attn"]["ntasks"] == 4 * 12 * 8 and ph["L3 attn bwd"]["ntasks"] == 2 * 4 * 12 * 8
+    assert ph["L0 qkv"]["ntasks"] == 32 * 18 and ph["L0 dWo"]["ntasks"] == 36 and ph["embed bwd wte"]["ntasks"] == 393
+    assert ph["adamw L5"]["ntasks"] == 109 and ph["adamw head"]["ntasks"] == 590 and ph["adamw wpe"]["ntasks"] == 12
+    assert 32 * 393 % ph["logits"]["ntasks"] == 0 or ph["logits"]["ntasks"] >= 32 * 393 // 4
+    order = ["wte", "wpe", "lm_head"] + [f"L{l}.{t}" for l in range(12) for t in ("g1", "Wqkv", "Wo", "g2", "Wup", "Wdn")] + ["gf"]
+    pos = 0
+    for n in order:
+        off, cnt = mk.param_span(n)
+        assert off == pos and off % 64 == 0
+        pos += cnt
+    assert pos == mk.num_params
+    mk.close()
+
+
+def test_serving_graph_is_a_chain(ofa):
+    mk = plan(ofa, "gpt_s", use_decode=1, infer_sms=24, reserved_sms=8, train_sms=116)
+    n = 3 * 12 + 2
+    for i in range(n):
+        deps = mk.phase_deps(i, job=1)
+        assert ((i - 1, 0) in deps) if i > 0 else deps == [(n - 1, -1)]
+    mk.close()
+
+
+@pytest.mark.parametrize("preset,kw", [("gpt_s", dict(dp_world=8, grad_bf16=1, ext_sync=1)), ("gpt_s", dict(dp_world=2, grad_bf16=1, ext_sync=1, tied_head=1)),
+                                       ("tiny", dict(dp_world=2, ext_sync=1, bucket_bytes=65536))])
+def test_gradient_buckets_partition_the_parameters(ofa, preset, kw):
+    mk = plan(ofa, preset, **kw)
+    b = mk.buckets()
+    assert len(b) >= 3 and ofa.dp.buckets_partition_params(b, mk.num_params)
+    names = [p["name"] for p in mk.phases()]
+    for i in range(len(b)):
+        r, w = names.index(f"grads ready {i}"), names.index(f"allreduce done {i}")
+        assert mk.phase_deps(w) == [(r, 0)]
+    # every AdamW phase is gated by exactly one all-reduce
+    for i, nm in enumerate(names):
+        if nm.startswith("adamw"):
+            deps = mk.phase_deps(i)
+            assert len(deps) == 1 and names[deps[0][0]].startswith("allreduce done")
+    mk.close()
+
+
+def test_planning_context_cannot_touch_a_device(ofa):
+    mk = plan(ofa, "tiny")
+    with pytest.raises(ofa.OfaError):
+        mk.launch(1)
+    with pytest.raises(ofa.OfaError):
+        mk.load_weights(np.zeros(mk.num_params, np.float32))
+    mk.close()
