@@ -154,15 +154,16 @@ def main():
     if args.impl == "reference":
         return run_reference(args, rank, world)
 
-    import torch
     ofa = importlib.import_module("open-flapping-airplanes_b200")
+    if world > 1:
+        ofa.dp.configure_env(8)                        # before the first CUDA call of the process
+    import torch
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the megakernel")
     torch.cuda.set_device(local_rank)
     dist = None
     if world > 1:
         import torch.distributed as dist
-        ofa.dp.configure_nccl_env(8)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     W, K = max(3, args.warmup), args.steps
     split = args.workload == "split"
@@ -200,9 +201,9 @@ def main():
         torch.cuda.synchronize()
 
     def run(n):
-        if dp is not None:
-            dp.enqueue(n)
         mk.launch(n)
+        if dp is not None:
+            dp.enqueue(n)                              # after the launch: a stream wait must never sit in front of the kernel that satisfies it
         mk.wait(600000)
         if dp is not None:
             dp.finish()

@@ -96,6 +96,8 @@ int ofa_set_starts(ofa_ctx* ctx, const uint32_t* starts, size_t nsteps);
  * OFA_TIMEOUT if it is still running after timeout_ms, OFA_DEVICE_ABORT if a bounded device wait expired. */
 int ofa_launch(ofa_ctx* ctx, int nsteps);
 int ofa_wait(ofa_ctx* ctx, int timeout_ms, ofa_status_t* status);
+/* asks a running launch to stop: the device's bounded waits see the request and the kernel returns (ofa_wait then reports OFA_DEVICE_ABORT). ofa_destroy does this itself, waits a few seconds and never blocks for good. */
+int ofa_abort(ofa_ctx* ctx);
 int ofa_steps_done(const ofa_ctx* ctx);                       /* total training steps completed by finished launches */
 float ofa_last_launch_ms(const ofa_ctx* ctx);                 /* CUDA-event time of the last finished launch */
 
@@ -120,7 +122,7 @@ int ofa_read_buffer(ofa_ctx* ctx, const char* name, void* out, size_t bytes);
 
 /* data-parallel hooks (no counterpart in the single-GPU reference): the gradient buffer (bf16 when grad_bf16, else fp32),
  * its buckets, and the two device flag arrays (int32 per bucket). The communication side waits until ready[b] >= s+1,
- * all-reduces bucket b in place, then stores s+1 to done[b], for every step s of a launch (flags restart at 0 per launch). */
+ * all-reduces bucket b in place, then stores s+1 to done[b], where s counts steps since ofa_create (ofa_steps_done() + the step's index in the launch): flag values only grow, so nothing needs resetting between launches. */
 int ofa_num_buckets(const ofa_ctx* ctx);
 int ofa_bucket_span(const ofa_ctx* ctx, int bucket, size_t* offset, size_t* count);   /* elements */
 void* ofa_grad_buffer(const ofa_ctx* ctx);

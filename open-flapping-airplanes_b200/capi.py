@@ -60,6 +60,7 @@ PROTOTYPES = {
     "ofa_set_starts": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t]),
     "ofa_launch": (C.c_int, [C.c_void_p, C.c_int]),
     "ofa_wait": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(Status)]),
+    "ofa_abort": (C.c_int, [C.c_void_p]),
     "ofa_steps_done": (C.c_int, [C.c_void_p]),
     "ofa_last_launch_ms": (C.c_float, [C.c_void_p]),
     "ofa_live": (C.c_int, [C.c_void_p, C.POINTER(LiveT)]),

@@ -113,13 +113,14 @@ __device__ __forceinline__ void run_train_task(const Ctx& C, const PhaseDesc& d,
       break;
     }
     case TK_EXT_SIGNAL:
-      if (threadIdx.x == 0) { __threadfence_system(); *reinterpret_cast<volatile int*>(d.p[0]) = step + 1; __threadfence_system(); }
+      // flag values count steps since the context was created, so a stale value from an earlier launch is always too small
+      if (threadIdx.x == 0) { __threadfence_system(); *reinterpret_cast<volatile int*>(d.p[0]) = C.step_base + step + 1; __threadfence_system(); }
       break;
     case TK_EXT_WAIT:
       if (threadIdx.x == 0) {
         const volatile int* flag = reinterpret_cast<const volatile int*>(d.p[0]);
         const u64 t0 = gtimer();
-        while (*flag < step + 1) {
+        while (*flag < C.step_base + step + 1) {
           if (aborted(C.status)) break;
           if (gtimer() - t0 > C.dep_timeout_ns) { raise_abort(C.status, ST_EXTERNAL_TIMEOUT, ph, local, step); break; }
           __nanosleep(200);

@@ -210,7 +210,7 @@ struct ofa_ctx {
   int* d_forced = nullptr; int* d_scal = nullptr;
   int* d_ext_ready = nullptr; int* d_ext_done = nullptr;   // device flags [32] each: gradients of bucket b ready / all-reduce of bucket b done
   std::vector<Span> buckets;
-  cudaStream_t stream = nullptr; cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  cudaStream_t stream = nullptr, abort_stream = nullptr; cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   bool dry = false;
   bool in_flight = false; int steps_total = 0, last_nsteps = 0; float last_ms = 0.f; int dec_steps_total = 0;
   std::string err;
@@ -573,11 +573,28 @@ extern "C" int ofa_default_config(ofa_config* cfg, const char* preset) {
 
 extern "C" const char* ofa_last_error(const ofa_ctx* ctx) { return ctx ? ctx->err.c_str() : g_create_error.c_str(); }
 
+// Host-requested abort: raises the grid-wide abort word; every bounded wait on the device sees it and the kernel returns.
+extern "C" int ofa_abort(ofa_ctx* c) {
+  if (!c || c->dry) return OFA_BAD_ARGUMENT;
+  if (!c->in_flight) return OFA_NOT_LAUNCHED;
+  cudaSetDevice(c->device);
+  static const int one = 1;
+  if (!c->abort_stream) cudaStreamCreateWithFlags(&c->abort_stream, cudaStreamNonBlocking);
+  cudaMemcpyAsync(&c->d_status->abort, &one, sizeof(int), cudaMemcpyHostToDevice, c->abort_stream);
+  return OFA_OK;
+}
+
 extern "C" void ofa_destroy(ofa_ctx* c) {
   if (!c) return;
   if (c->dry) { delete c; return; }
   cudaSetDevice(c->device);
-  if (c->in_flight) cudaStreamSynchronize(c->stream);
+  if (c->in_flight) {
+    // never block forever: ask the kernel to drain, give it a few seconds, and otherwise leak the device memory it may still use
+    ofa_abort(c);
+    bool done = false;
+    for (int i = 0; i < 25000 && !done; i++) { done = cudaEventQuery(c->ev1) != cudaErrorNotReady; if (!done) { struct timespec sl = {0, 200000}; nanosleep(&sl, nullptr); } }
+    if (!done) { delete c; return; }
+  }
   c->train_job.free_all(); c->dec_job.free_all();
   c->ar.free_all();
   if (c->h_live) cudaFreeHost(c->h_live);
@@ -585,6 +602,7 @@ extern "C" void ofa_destroy(ofa_ctx* c) {
   if (c->ev0) cudaEventDestroy(c->ev0);
   if (c->ev1) cudaEventDestroy(c->ev1);
   if (c->stream) cudaStreamDestroy(c->stream);
+  if (c->abort_stream) cudaStreamDestroy(c->abort_stream);
   delete c;
 }
 
@@ -791,7 +809,6 @@ extern "C" int ofa_launch(ofa_ctx* c, int nsteps) {
   C.step_base = c->steps_total;
   cudaMemsetAsync(c->d_status, 0, sizeof(DevStatus), c->stream);
   cudaMemsetAsync(c->d_finished, 0, sizeof(int), c->stream);
-  cudaMemsetAsync(c->d_ext_ready, 0, 64 * sizeof(int), c->stream);
   cudaMemsetAsync(c->d_phase_busy, 0, sizeof(unsigned long long) * std::max<size_t>(1, c->train_ph.size()), c->stream);
   C.smem_bytes = c->smem;
   const Ctx& L = C;

@@ -33,8 +33,8 @@ enum TaskKind : int {
   TK_DEC_UPDN,
   TK_DEC_HEAD,
   TK_DEC_SAMPLE,
-  TK_EXT_WAIT,     // 1 task: wait (bounded) until an external 32-bit flag >= step+1 (gradient all-reduce finished)
-  TK_EXT_SIGNAL,   // 1 task: store step+1 to an external 32-bit flag (gradient bucket ready)
+  TK_EXT_WAIT,     // 1 task: wait (bounded) until an external 32-bit flag >= step_base+step+1 (gradient all-reduce finished)
+  TK_EXT_SIGNAL,   // 1 task: store step_base+step+1 to an external 32-bit flag (gradient bucket ready)
   TK_COUNT
 };
 

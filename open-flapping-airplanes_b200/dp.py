@@ -1,24 +1,34 @@
 """Data-parallel driver: bucketed gradient all-reduce over NCCL, ordered against the persistent megakernel by device flags
 only. The reference is single-GPU (no collective anywhere in it); this is the multi-GPU plumbing of this library.
 
-Per rank, the megakernel raises ready[b] = s+1 (a 1-task phase of its graph) once every gradient of bucket b of step s is
-written, and holds that bucket's AdamW phases behind a bounded wait for done[b] >= s+1. This module enqueues, for every
-step and bucket of a launch, on one communication stream and BEFORE the launch:
-    cuStreamWaitValue32(ready[b] >= s+1)  ->  all_reduce(bucket b, sum, in place)  ->  cuStreamWriteValue32(done[b] = s+1)
+Per rank, the megakernel raises ready[b] = g+1 (a 1-task phase of its graph; g = global step index since the context was
+created) once every gradient of bucket b of that step is written, and holds the bucket's AdamW phases behind a bounded wait
+for done[b] >= g+1. For every step and bucket of a launch this module enqueues on one communication stream
+    cuStreamWaitValue32(ready[b] >= g+1)  ->  all_reduce(bucket b, sum, in place)  ->  cuStreamWriteValue32(done[b] = g+1)
 so no host thread sits in the loop while the kernel runs. The sum is not divided here: AdamW folds 1/world into its read of
-the gradient. NCCL's blocks run on the SMs the megakernel leaves unoccupied (the reserved partition), so the number of NCCL
-channels must not exceed what fits there: `configure_nccl_env()` caps it before the process group is created.
+the gradient.
+
+Two rules keep this free of false dependencies:
+  * enqueue AFTER the launch (`mk.launch(n); dp.enqueue(n)`): a stream-wait that sits at the head of a hardware queue blocks
+    every stream mapped to that queue, and it must never be able to block the launch of the kernel that will satisfy it;
+    `configure_env()` also raises CUDA_DEVICE_MAX_CONNECTIONS so that streams rarely share a queue;
+  * NCCL's blocks run on the SMs the megakernel leaves unoccupied (the reserved partition), so the number of NCCL channels
+    must not exceed what fits there: `configure_env()` caps it before the process group is created.
+If the communication side never answers, the device-side wait expires and the launch returns OFA_DEVICE_ABORT.
 """
-import ctypes as C
 import os
 
 import numpy as np
 
 
-def configure_nccl_env(reserved_sms=8):
-    """Call before torch.distributed.init_process_group. Keeps NCCL's resident blocks within the reserved SM partition."""
+def configure_env(reserved_sms=8):
+    """Call before the first CUDA call of the process and before torch.distributed.init_process_group."""
     os.environ.setdefault("NCCL_MAX_CTAS", str(max(1, reserved_sms)))
     os.environ.setdefault("NCCL_MIN_CTAS", "1")
+    os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")
+
+
+configure_nccl_env = configure_env
 
 
 def bucket_schedule(buckets, nsteps):
@@ -69,28 +79,34 @@ class DataParallel:
             self.grad = raw.view(torch.bfloat16)
         else:
             self.grad = torch.as_tensor(_DevArray(gptr, n, "<f4"), device="cuda")
+        if self.grad.data_ptr() != gptr:
+            raise RuntimeError("torch copied the gradient buffer instead of aliasing it")
         self.ready_ptr, self.done_ptr = mk.ext_flags_ptrs()
         self.stream = stream if stream is not None else torch.cuda.Stream()
-        self._zeros = np.zeros(64, dtype=np.int32)
+        # first collective on the communication stream now: communicator set-up and its allocations must not happen while
+        # a persistent kernel is resident
+        with torch.cuda.stream(self.stream):
+            warm = torch.zeros(1024, device="cuda", dtype=self.grad.dtype)
+            dist.all_reduce(warm)
+        self.stream.synchronize()
 
     def _check(self, res):
         err = res[0] if isinstance(res, tuple) else res
         if int(err) != 0:
             raise RuntimeError(f"CUDA driver call failed: {err}")
 
-    def enqueue(self, nsteps):
-        """Queue the whole launch's communication. The previous launch must have finished (its flags are cleared here)."""
-        from . import capi
-        capi.load().ofa_h2d(C.c_void_p(self.ready_ptr), self._zeros.ctypes.data_as(C.c_void_p), self._zeros.nbytes)
+    def enqueue(self, nsteps, first_step=None):
+        """Queue the communication of a launch of `nsteps` steps. Call right AFTER mk.launch(nsteps)."""
         torch, cu = self.torch, self.cu
+        base = self.mk.steps_done if first_step is None else first_step
         h = cu.CUstream(self.stream.cuda_stream)
         geq = cu.CUstreamWaitValue_flags.CU_STREAM_WAIT_VALUE_GEQ
         with torch.cuda.stream(self.stream):
             for s, b in bucket_schedule(self.buckets, nsteps):
                 off, cnt = self.buckets[b]
-                self._check(cu.cuStreamWaitValue32(h, self.ready_ptr + 4 * b, s + 1, geq))
+                self._check(cu.cuStreamWaitValue32(h, self.ready_ptr + 4 * b, base + s + 1, geq))
                 self.dist.all_reduce(self.grad[off:off + cnt])
-                self._check(cu.cuStreamWriteValue32(h, self.done_ptr + 4 * b, s + 1, 0))
+                self._check(cu.cuStreamWriteValue32(h, self.done_ptr + 4 * b, base + s + 1, 0))
 
     def finish(self):
         self.stream.synchronize()

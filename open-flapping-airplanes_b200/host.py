@@ -111,6 +111,9 @@ class Megakernel:
         if rc != capi.OK:
             raise OfaError(rc, "timeout" if rc == capi.TIMEOUT else self.lib.ofa_last_error(self.h).decode(), st)
 
+    def abort(self):
+        return self.lib.ofa_abort(self.h)
+
     def run(self, nsteps, timeout_ms=600000):
         self.launch(nsteps); self.wait(timeout_ms)
         return self.lib.ofa_last_launch_ms(self.h)

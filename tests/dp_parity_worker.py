@@ -18,8 +18,8 @@ def main():
     from oracle import gpt_oracle as orc
     ofa = importlib.import_module("open-flapping-airplanes_b200")
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    ofa.dp.configure_env(8)                        # before the first CUDA call
     torch.cuda.set_device(local)
-    ofa.dp.configure_nccl_env(8)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     nsteps, V, L, T, B = 6, 1024, 2, 256, 2
     ocfg = orc.OracleConfig(V=V, D=768, L=L, H=12, T=T, B=B, tied=False)
@@ -34,7 +34,7 @@ def main():
     mk.load_weights(orc.flatten(ocfg, w0)); mk.set_tokens(tokens); mk.set_starts(starts.astype(np.uint32))
     dp = ofa.dp.DataParallel(mk, dist)
     for n in (2, nsteps - 2):                      # two launches: the flags restart, the optimizer state continues
-        dp.enqueue(n); mk.launch(n); mk.wait(120000); dp.finish()
+        mk.launch(n); dp.enqueue(n); mk.wait(60000); dp.finish()
     losses = torch.tensor(mk.losses(), dtype=torch.float64, device="cuda")
     dist.all_reduce(losses); losses /= world
     w = torch.from_numpy(mk.read_weights()).cuda()

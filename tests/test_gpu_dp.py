@@ -1,6 +1,7 @@
 """Data parallelism on real GPUs (needs at least two): one process per GPU over NCCL, gradients all-reduced bucket by
 bucket while the persistent kernels run, ordered only by device flags. Skipped on a single-GPU box."""
 import os
+import signal
 import subprocess
 import sys
 
@@ -16,5 +17,11 @@ def test_two_rank_training_matches_global_batch_oracle():
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1", "--master-port", "29617",
            os.path.join(ROOT, "tests", "dp_parity_worker.py")]
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
-    assert r.returncode == 0 and "DP_PARITY_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+    p = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=env, start_new_session=True)
+    try:
+        out, err = p.communicate(timeout=240)
+    except subprocess.TimeoutExpired:
+        os.killpg(p.pid, signal.SIGKILL)          # the whole process group this test started, nothing else
+        out, err = p.communicate()
+        pytest.fail("data-parallel worker timed out\n" + out[-2000:] + err[-2000:])
+    assert p.returncode == 0 and "DP_PARITY_OK" in out, out[-3000:] + err[-3000:]
