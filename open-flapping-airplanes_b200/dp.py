@@ -25,6 +25,7 @@ def configure_env(reserved_sms=8):
     """Call before the first CUDA call of the process and before torch.distributed.init_process_group."""
     os.environ.setdefault("NCCL_MAX_CTAS", str(max(1, reserved_sms)))
     os.environ.setdefault("NCCL_MIN_CTAS", "1")
+    os.environ.setdefault("NCCL_CGA_CLUSTER_SIZE", "0")     # no thread-block clusters: a cluster needs several free SMs of one GPC at once
     os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")
 
 

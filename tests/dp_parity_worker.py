@@ -14,13 +14,25 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 
 
+def log(msg):
+    """progress lines (flushed) so that a run that is cut short still shows how far it got"""
+    path = os.environ.get("OFA_DP_LOG")
+    line = f"[rank {os.environ.get('RANK', '?')}] {msg}"
+    if path:
+        with open(f"{path}.rank{os.environ.get('RANK', '0')}.log", "a") as f:
+            f.write(line + "\n")
+    print(line, flush=True)
+
+
 def main():
     from oracle import gpt_oracle as orc
     ofa = importlib.import_module("open-flapping-airplanes_b200")
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     ofa.dp.configure_env(8)                        # before the first CUDA call
     torch.cuda.set_device(local)
+    log("init_process_group")
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    log("process group up")
     nsteps, V, L, T, B = 6, 1024, 2, 256, 2
     ocfg = orc.OracleConfig(V=V, D=768, L=L, H=12, T=T, B=B, tied=False)
     w0 = orc.init_weights(ocfg)
@@ -32,9 +44,11 @@ def main():
     cfg.device, cfg.dp_world, cfg.grad_bf16, cfg.ext_sync, cfg.reserved_sms, cfg.bucket_bytes = local, world, 1, 1, 8, 8 << 20
     mk = ofa.Megakernel(cfg)
     mk.load_weights(orc.flatten(ocfg, w0)); mk.set_tokens(tokens); mk.set_starts(starts.astype(np.uint32))
+    log("context created, buckets %s" % (mk.buckets(),))
     dp = ofa.dp.DataParallel(mk, dist)
+    log("communication stream warmed up")
     for n in (2, nsteps - 2):                      # two launches: the flags restart, the optimizer state continues
-        mk.launch(n); dp.enqueue(n); mk.wait(60000); dp.finish()
+        mk.launch(n); log(f"launched {n}"); dp.enqueue(n); log("enqueued"); mk.wait(60000); log("kernel done"); dp.finish(); log("comm done")
     losses = torch.tensor(mk.losses(), dtype=torch.float64, device="cuda")
     dist.all_reduce(losses); losses /= world
     w = torch.from_numpy(mk.read_weights()).cuda()
