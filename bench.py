@@ -264,6 +264,8 @@ def main():
             "clocks": clocks,
         }
         if args.phase_table:
+            bb = mk.block_busy_ns()
+            print(f"  blocks that ran training tasks: {(bb[:, 0] > 0).sum()}, serving tasks: {(bb[:, 1] > 0).sum()}; mean training-block busy {bb[:, 0][bb[:, 0] > 0].mean() / 1e6 / K:.3f} ms/step", file=sys.stderr)
             tot = sum(p["busy_ns"] for p in mk.phases()) or 1
             for p in sorted(mk.phases(), key=lambda p: -p["busy_ns"])[:40]:
                 print(f"  {p['name']:24s} tasks {p['ntasks']:6d}  busy {p['busy_ns'] / 1e6 / K:8.3f} ms/step  {100.0 * p['busy_ns'] / tot:5.1f} %", file=sys.stderr)

@@ -110,6 +110,14 @@ int ofa_read_losses(ofa_ctx* ctx, float* out, size_t n);                  /* los
 int ofa_read_step_times(ofa_ctx* ctx, unsigned long long* out, size_t n); /* %globaltimer ns at the end of each step of the last launch */
 int ofa_num_phases(const ofa_ctx* ctx);
 int ofa_phase_info(const ofa_ctx* ctx, int phase, char* name, size_t name_cap, int* kind, int* ntasks, unsigned long long* busy_ns);
+/* busy nanoseconds of every block in the last launch: out[2*block + job] (job 0 training, 1 serving), n <= 2 * grid size (ofa.cu:313 blk_busy) */
+int ofa_read_block_busy(ofa_ctx* ctx, unsigned long long* out, size_t n);
+/* in-kernel trace of the serving job (the reference's DTRACE, decode_wide.cuh:11-16): %globaltimer stamps of the stage boundaries inside task 0 of layer 0 (slots 0-4 QKV, 8-12 UP+DOWN, 16-19 scheduler-side start/end of those tasks), last token of the last launch */
+int ofa_read_decode_trace(ofa_ctx* ctx, unsigned long long* out, size_t n);
+/* where each block of the last launch ran and as what: out[block] = %smid | role << 16, role 1 serving, 2 reserved (idle), 3 training, 4 idle (ofa_kernel's role dispatch, ofa.cu:316-326) */
+int ofa_read_block_info(ofa_ctx* ctx, int* out, size_t n);
+/* serving-graph counterpart of ofa_phase_info: summed task time of a decode phase during the last launch; returns OFA_BAD_ARGUMENT past the last phase */
+int ofa_decode_phase_info(const ofa_ctx* ctx, int phase, char* name, size_t name_cap, int* ntasks, unsigned long long* busy_ns);
 /* dependencies of a phase: job 0 = training graph, 1 = serving graph; returns their number and fills up to cap (phase, step-delta) pairs (Job::deps, ofa.cu:103-105) */
 int ofa_phase_deps(const ofa_ctx* ctx, int job, int phase, int* dep_phase, int* dep_delta, int cap);
 int ofa_decode_steps(const ofa_ctx* ctx);                                  /* tokens processed by the serving job      */

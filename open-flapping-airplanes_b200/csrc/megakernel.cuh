@@ -133,18 +133,41 @@ __device__ __forceinline__ void run_train_task(const Ctx& C, const PhaseDesc& d,
 }
 
 template <class T, int D, int DH>
-__device__ __forceinline__ void run_decode_task(const Ctx& C, const PhaseDesc& d, int local, unsigned char* smem) {
+__device__ __forceinline__ void run_decode_task(const Ctx& C, const PhaseDesc& d, int local, unsigned char* smem, uint32_t bar, uint32_t parity) {
   switch (d.kind) {
-    case TK_DEC_QKV: dec::task_qkv<T, D, DH>(C.dp, C.md, d.i0, local, smem); break;
-    case TK_DEC_ATTWO: dec::task_attwo<T, D, DH>(C.dp, C.md, d.i0, local, smem); break;
-    case TK_DEC_UPDN: dec::task_updn<T, D, DH>(C.dp, C.md, d.i0, local, smem); break;
-    case TK_DEC_HEAD: dec::task_head<T, D, DH>(C.dp, C.md, local, smem); break;
+    case TK_DEC_QKV: dec::task_qkv<T, D, DH>(C.dp, C.md, d.i0, local, smem, bar, parity, C.status); break;
+    case TK_DEC_ATTWO: dec::task_attwo<T, D, DH>(C.dp, C.md, d.i0, local, smem, bar, parity, C.status); break;
+    case TK_DEC_UPDN: dec::task_updn<T, D, DH>(C.dp, C.md, d.i0, local, smem, bar, parity, C.status); break;
+    case TK_DEC_HEAD: dec::task_head<T, D, DH>(C.dp, C.md, local, smem, bar, parity, C.status); break;
     case TK_DEC_SAMPLE: dec::task_sample<T, D, DH>(C.dp, C.md, C.live, smem); break;
     default: break;
   }
 }
 
 // ---------------------------------------------------------------------------------------------- scheduler
+// Dependency wait of thread 0 (bounded). Returns 0 when every dependency of (step, ph) is satisfied, -2 when the block must
+// leave (job finished elsewhere, abort, or deadline).
+__device__ __forceinline__ int wait_deps(const Ctx& C, const Job& J, int job_id, int step, int ph, int local) {
+  const int off = __ldg(J.dep_off + ph), cnt = __ldg(J.dep_cnt + ph);
+  const u64 t0 = gtimer();
+  unsigned spins = 0;
+  for (;;) {
+    bool ready = true;
+    for (int k = 0; k < cnt && ready; k++) {
+      const Dep e = J.deps[off + k];
+      const int need = __ldg(J.ntasks + e.phase) * (step + 1 + e.delta);
+      if (need > 0 && ld_acquire(J.done + e.phase) < need) ready = false;
+    }
+    if (ready) return 0;
+    if (job_id == 1 && C.use_train && ld_relaxed(C.finished)) return -2;
+    if ((++spins & 63u) == 0) {
+      if (aborted(C.status)) return -2;
+      if (gtimer() - t0 > C.dep_timeout_ns) { raise_abort(C.status, ST_DEP_TIMEOUT, ph, local, step); return -2; }
+    }
+    __nanosleep(job_id == 1 ? 20 : 80);
+  }
+}
+
 template <class T, int D, int DH>
 __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* smem) {
   volatile int* s_sel = reinterpret_cast<volatile int*>(smem + C.smem_bytes - 128);   // the last 256 bytes of dynamic shared memory are the block's control area
@@ -155,8 +178,15 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
   gemm_tc::GemmPipe gp; gp.stage_count = gp.tile_count = gp.tmem_base = 0;
   const bool use_tc = IsBf16<T>::value && job_id == 0;
   if (use_tc) gemm_tc::block_init(gp, smem, C.status);
+  // serving blocks: one mbarrier counts the bytes of the weight prefetch of the task they hold a ticket for
+  const uint32_t fill_bar = smem_u32(smem + C.smem_bytes - 256 + 96);
+  uint32_t fills = 0;
+  if (job_id == 1) {
+    if (tid == 0) { mbar_init(fill_bar, 1); mbar_fence_init(); }
+    __syncthreads();
+  }
   for (;;) {
-    if (tid == 0) {
+    if (tid == 0) {                                  // ---- claim (and, for the training job, wait for the dependencies)
       int res = 0, step = 0, ph = 0, local = 0;
       if (aborted(C.status) || (job_id == 1 && C.use_train && ld_relaxed(C.finished))) res = -2;
       else {
@@ -168,49 +198,56 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
           int lo = 0, hi = J.nph;                   // last phase whose prefix <= r
           while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if (__ldg(J.prefix + mid) <= r) lo = mid; else hi = mid; }
           ph = lo; local = r - __ldg(J.prefix + ph);
-          if (!(step == rstep && ph == rph)) {
-            const int off = __ldg(J.dep_off + ph), cnt = __ldg(J.dep_cnt + ph);
-            const u64 t0 = gtimer();
-            unsigned spins = 0;
-            for (;;) {
-              bool ready = true;
-              for (int k = 0; k < cnt && ready; k++) {
-                const Dep e = J.deps[off + k];
-                const int need = __ldg(J.ntasks + e.phase) * (step + 1 + e.delta);
-                if (need > 0 && ld_acquire(J.done + e.phase) < need) ready = false;
-              }
-              if (ready) { rstep = step; rph = ph; break; }
-              if (job_id == 1 && C.use_train && ld_relaxed(C.finished)) { res = -2; break; }
-              if ((++spins & 63u) == 0) {
-                if (aborted(C.status)) { res = -2; break; }
-                if (gtimer() - t0 > C.dep_timeout_ns) { raise_abort(C.status, ST_DEP_TIMEOUT, ph, local, step); res = -2; break; }
-              }
-              __nanosleep(job_id == 1 ? 40 : 80);
-            }
+          if (job_id == 0 && !(step == rstep && ph == rph)) {
+            res = wait_deps(C, J, job_id, step, ph, local);
+            if (res == 0) { rstep = step; rph = ph; }
           }
         }
       }
       s_sel[0] = res; s_sel[1] = step; s_sel[2] = ph; s_sel[3] = local;
     }
     __syncthreads();
-    const int res = s_sel[0], step = s_sel[1], ph = s_sel[2], local = s_sel[3];
-    __syncthreads();
+    int res = s_sel[0];
+    const int step = s_sel[1], ph = s_sel[2], local = s_sel[3];
     if (res < 0) break;
     const PhaseDesc& d = J.ph[ph];
+    bool filled = false;
+    if (job_id == 1) {                               // ---- serving: start the weight prefetch, THEN wait for the dependencies
+      filled = dec::prefetch<T, D, DH>(C.dp, C.md, d.kind, d.i0, local, smem, fill_bar);
+      if (tid == 0) {
+        int r2 = 0;
+        if (!(step == rstep && ph == rph)) { r2 = wait_deps(C, J, job_id, step, ph, local); if (r2 == 0) { rstep = step; rph = ph; } }
+        s_sel[4] = r2;
+      }
+      __syncthreads();
+      res = s_sel[4];
+      if (res < 0) {                                 // leaving with copies in flight: give them a bounded chance to land
+        if (filled) mbar_wait(fill_bar, fills & 1u, C.status);
+        __syncthreads();
+        break;
+      }
+    } else {
+      __syncthreads();                               // s_sel may be rewritten by thread 0 only after everyone has read it
+    }
     u64 t0 = 0;
-    if (tid == 0) t0 = gtimer();
+    if (tid == 0) { t0 = gtimer(); if (job_id == 1 && C.dp.trace && local == 0 && (ph == 0 || ph == 2)) C.dp.trace[16 + ph] = t0; }
     if (job_id == 0) run_train_task<T, D, DH>(C, d, ph, local, step, smem, gp);
-    else run_decode_task<T, D, DH>(C, d, local, smem);
+    else run_decode_task<T, D, DH>(C, d, local, smem, fill_bar, fills & 1u);
+    if (filled) fills++;
     __threadfence();
     __syncthreads();
     if (tid == 0) {
       const u64 t1 = gtimer();
+      if (job_id == 1 && C.dp.trace && local == 0 && (ph == 0 || ph == 2)) C.dp.trace[17 + ph] = t1;
       busy += t1 - t0;
       if (job_id == 0 && C.phase_busy) {
         atomicAdd(C.phase_busy + ph, t1 - t0);
         if (step == C.prof_step) { atomicMin(C.phase_first + ph, t0); atomicMax(C.phase_last + ph, t1); }
       }
-      const int old = atomicAdd(J.done + ph, 1);
+      if (job_id == 1 && C.dec_phase_busy) atomicAdd(C.dec_phase_busy + ph, t1 - t0);
+      int old = -1;
+      if (ph == J.last_phase) old = atomicAdd(J.done + ph, 1);
+      else red_release_add(J.done + ph, 1);            // no return value needed: do not wait for the round trip
       if (ph == J.last_phase && old == __ldg(J.ntasks + ph) * (step + 1) - 1) {     // last task of the step
         if (job_id == 0) {
           C.step_done[step] = t1;
@@ -224,17 +261,34 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
   if (tid == 0 && C.blk_busy) C.blk_busy[blockIdx.x * 2 + job_id] = busy;
 }
 
-// Role of a block = the partition its SM falls into: [0, infer) serve, [infer, infer+reserved) idle (left free for
-// collectives), the next train_sms train, the rest idle.
+// A block of an idle partition must not leave before the whole grid has been placed: the hardware refills the slot of an
+// exited block first, so early exits would steal the second block of the working SMs (measured: the 24-SM serving partition
+// ran with one block per SM). Idle blocks therefore wait (bounded) until every block of the grid has reported in.
+__device__ __forceinline__ void idle_block(const Ctx& C) {
+  if (threadIdx.x == 0 && C.arrived) {
+    const u64 t0 = gtimer();
+    while (ld_relaxed(C.arrived) < (int)gridDim.x && gtimer() - t0 < 20000000ull) __nanosleep(500);
+  }
+}
+
 template <class T, int D, int DH>
 __global__ void __launch_bounds__(NTHR, 2) ofa_kernel(const __grid_constant__ Ctx C) {
   extern __shared__ __align__(1024) unsigned char dsm[];
   const unsigned hw = smid();
   const int rank = C.smid_rank ? C.smid_rank[hw] : (int)hw;
   const int isms = C.use_decode ? C.infer_sms : 0;
-  if (rank < isms) job_loop<T, D, DH>(C, C.dec, 1, dsm);
-  else if (rank < isms + C.reserved_sms) return;
-  else if (rank < isms + C.reserved_sms + C.train_sms) { if (C.use_train) job_loop<T, D, DH>(C, C.train, 0, dsm); }
+  if (threadIdx.x == 0 && C.arrived) atomicAdd(C.arrived, 1);
+  const int role = rank < isms ? 1 : rank < isms + C.reserved_sms ? 2 : (rank < isms + C.reserved_sms + C.train_sms && C.use_train) ? 3 : 4;
+  if (threadIdx.x == 0 && C.blk_info) C.blk_info[blockIdx.x] = (int)hw | (role << 16);
+  if constexpr (IsBf16<T>::value) {
+    // Blocks that never allocate TMEM give up their allocation permit at once. Measured on B200: while a resident block of a
+    // kernel that contains tcgen05.alloc still holds the permit, the hardware does not place a second block of that kernel on
+    // the SM; the serving partition ran with one block per SM (24 instead of 48 blocks) until this line was added.
+    if (role != 3 && threadIdx.x < 32) asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (role == 1) job_loop<T, D, DH>(C, C.dec, 1, dsm);
+  else if (role == 3) job_loop<T, D, DH>(C, C.train, 0, dsm);
+  else idle_block(C);
 }
 
 // one resident block per slot records its %smid so the host can build a dense rank table

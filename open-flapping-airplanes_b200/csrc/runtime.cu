@@ -69,14 +69,16 @@ EncodeFn get_encode() {
   }
   return enc;
 }
-// 2-D bf16 tensor map, SWIZZLE_128B: `inner` contiguous elements, `outer` rows of `ld` elements, box {box_inner, box_outer}
-bool encode_map(CUtensorMap* m, const void* base, uint64_t inner, uint64_t outer, uint64_t ld, uint32_t box_inner, uint32_t box_outer) {
+// 2-D tensor map: `inner` contiguous elements, `outer` rows of `ld` elements, box {box_inner, box_outer}. GEMM operands are
+// bf16 with SWIZZLE_128B; the serving job's weight prefetch uses plain (unswizzled) views in the activation type.
+bool encode_map(CUtensorMap* m, const void* base, uint64_t inner, uint64_t outer, uint64_t ld, uint32_t box_inner, uint32_t box_outer,
+                bool is_f32 = false, bool swizzle = true) {
   EncodeFn enc = get_encode();
   if (!enc) return false;
-  cuuint64_t dims[2] = {inner, outer}, strides[1] = {ld * 2};
+  cuuint64_t dims[2] = {inner, outer}, strides[1] = {ld * (is_f32 ? 4u : 2u)};
   cuuint32_t box[2] = {box_inner, box_outer}, es[2] = {1, 1};
-  return enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  return enc(m, is_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 struct Arena {   // device allocations owned by one context / one ofa_run_phases call
@@ -169,6 +171,9 @@ bool upload_job(const std::vector<HostPhase>& ph, int last_phase, int nsteps, De
 template <class T, int D, int DH> cudaError_t launch_kernel(const Ctx& C, int nblocks, int smem, cudaStream_t s) {
   cudaError_t e = cudaFuncSetAttribute(ofa_kernel<T, D, DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
+  // ask for the largest shared-memory carve-out on every SM: with a smaller split an SM holds one 113 KB block instead of two,
+  // and a persistent block never leaves to let the split be changed (measured: 24 SMs ran with a single block)
+  cudaFuncSetAttribute(ofa_kernel<T, D, DH>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
   ofa_kernel<T, D, DH><<<nblocks, NTHR, smem, s>>>(C);
   return cudaGetLastError();
 }
@@ -204,6 +209,7 @@ struct ofa_ctx {
   int* d_finished = nullptr; unsigned long long* d_t_end = nullptr;
   unsigned long long *d_phase_busy = nullptr, *d_phase_first = nullptr, *d_phase_last = nullptr, *d_step_done = nullptr, *d_blk_busy = nullptr;
   float* d_loss_hist = nullptr; int loss_cap = 0;
+  unsigned long long* d_dec_phase_busy = nullptr; int* d_blk_info = nullptr;
   int* d_smid_rank = nullptr;
   Live* h_live = nullptr; Live* d_live = nullptr;
   int* h_out = nullptr; int* d_out = nullptr; int out_cap = 0;
@@ -478,6 +484,20 @@ bool build_decode_graph(ofa_ctx* c) {
   for (int l = 0; l < L; l++) { hq[l] = Wact + lay.wqkv[l]; ho[l] = Wact + lay.wo[l]; hu[l] = Wact + lay.wup[l]; hd[l] = Wact + lay.wdn[l]; h1[l] = Wact + lay.g1[l]; h2[l] = Wact + lay.g2[l]; }
   auto up = [&](const std::vector<const void*>& h) { const void** d = c->ar.alloc<const void*>(L); if (d) c->ar.h2d(d, h.data(), L * sizeof(void*)); return (const void* const*)d; };
   dp.wqkv = up(hq); dp.wo = up(ho); dp.wup = up(hu); dp.wdn = up(hd); dp.g1 = up(h1); dp.g2 = up(h2);
+  {  // unswizzled 2-D views for the weight prefetch: one 64-column (QKV) / 32-column (up) / head-by-column-block (Wo) box per copy
+    const bool f32w = !c->bf;
+    const uint32_t brow = D < 256 ? D : 256, cbw = D < 256 ? D : 256;
+    std::vector<CUtensorMap> mq(L), mu(L), mo(L);
+    bool okm = true;
+    for (int l = 0; l < L && !c->ar.dry; l++) {
+      okm = okm && encode_map(&mq[l], hq[l], 3 * D, D, 3 * D, 64, brow, f32w, false) && encode_map(&mu[l], hu[l], m.FF, D, m.FF, dec::HU, brow, f32w, false) &&
+            encode_map(&mo[l], ho[l], D, D, D, cbw, m.DH, f32w, false);
+    }
+    if (!okm) { c->err = "cuTensorMapEncodeTiled failed (decode prefetch views)"; return false; }
+    CUtensorMap* dq = c->ar.alloc<CUtensorMap>(L, false); CUtensorMap* du = c->ar.alloc<CUtensorMap>(L, false); CUtensorMap* dw = c->ar.alloc<CUtensorMap>(L, false);
+    if (dq && du && dw) { c->ar.h2d(dq, mq.data(), L * sizeof(CUtensorMap)); c->ar.h2d(du, mu.data(), L * sizeof(CUtensorMap)); c->ar.h2d(dw, mo.data(), L * sizeof(CUtensorMap)); }
+    dp.tm_qkv = dq; dp.tm_up = du; dp.tm_wo = dw;
+  }
   DecodeState& st = dp.st;
   st.xw = c->ar.alloc<unsigned long long>(D); st.xr = c->ar.alloc<unsigned long long>(D);
   st.q = c->ar.alloc<T>(D);
@@ -494,6 +514,7 @@ bool build_decode_graph(ofa_ctx* c) {
   }
   st.out_tokens = c->d_out; st.out_cap = c->out_cap;
   c->d_forced = c->ar.alloc<int>(std::max(1, cfg.n_prompt));
+  dp.trace = c->ar.alloc<unsigned long long>(64);
   if (!c->ar.ok) { c->err = "out of device memory (decode state)"; return false; }
   c->ar.h2d(c->d_forced, cfg.prompt, sizeof(int) * cfg.n_prompt);
   dp.forced = c->d_forced; dp.nforced = cfg.n_prompt; dp.answer_len = cfg.answer_len; dp.auto_reset = 1;
@@ -512,7 +533,7 @@ bool build_decode_graph(ofa_ctx* c) {
     const std::string s = "dec L" + std::to_string(l) + " ";
     mk(s + "qkv", TK_DEC_QKV, 3 * D / 64, l);
     mk(s + "att+wo", TK_DEC_ATTWO, m.H * (D / CB), l);
-    mk(s + "up+down", TK_DEC_UPDN, m.FF / 64, l);
+    mk(s + "up+down", TK_DEC_UPDN, m.FF / dec::HU, l);
   }
   mk("dec head", TK_DEC_HEAD, nchunk, 0);
   mk("dec sample", TK_DEC_SAMPLE, 1, 0);
@@ -525,6 +546,7 @@ bool probe_smids(ofa_ctx* c) {
   unsigned* seen = c->ar.alloc<unsigned>(64);
   if (!seen) return false;
   cudaFuncSetAttribute(smid_probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, c->smem);
+  cudaFuncSetAttribute(smid_probe_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
   smid_probe_kernel<<<c->nblocks, NTHR, c->smem, c->stream>>>(seen);
   if (cudaStreamSynchronize(c->stream) != cudaSuccess) return false;
   unsigned h[64]; cudaMemcpy(h, seen, sizeof h, cudaMemcpyDeviceToHost);
@@ -663,7 +685,7 @@ extern "C" int ofa_create(const ofa_config* cfg, ofa_ctx** out) {
   c->W32 = c->ar.alloc<float>(NP); c->M32 = c->ar.alloc<float>(NP); c->V32 = c->ar.alloc<float>(NP);
   c->Wact = c->bf ? (void*)c->ar.alloc<bf16>(NP) : (void*)c->ar.alloc<float>(NP);
   if (cfg->grad_bf16) c->Gbf = c->ar.alloc<bf16>(NP); else c->G32 = c->ar.alloc<float>(NP);
-  c->d_status = c->ar.alloc<DevStatus>(1); c->d_finished = c->ar.alloc<int>(1); c->d_t_end = c->ar.alloc<unsigned long long>(1);
+  c->d_status = c->ar.alloc<DevStatus>(1); c->d_finished = c->ar.alloc<int>(2); c->d_t_end = c->ar.alloc<unsigned long long>(1);
   if (!c->ar.ok) return bail(OFA_CUDA_ERROR, "out of device memory (parameters)");
   if (!dry) {
     if (cudaHostAlloc(&c->h_live, sizeof(Live), cudaHostAllocMapped) != cudaSuccess) return bail(OFA_CUDA_ERROR, "cudaHostAlloc failed");
@@ -693,7 +715,9 @@ extern "C" int ofa_create(const ofa_config* cfg, ofa_ctx** out) {
   c->d_phase_busy = c->ar.alloc<unsigned long long>(nph); c->d_phase_first = c->ar.alloc<unsigned long long>(nph); c->d_phase_last = c->ar.alloc<unsigned long long>(nph);
   c->d_blk_busy = c->ar.alloc<unsigned long long>(2 * c->nblocks);
   if (!c->ar.ok) return bail(OFA_CUDA_ERROR, "out of device memory");
-  C.phase_busy = c->d_phase_busy; C.phase_first = c->d_phase_first; C.phase_last = c->d_phase_last; C.blk_busy = c->d_blk_busy;
+  c->d_dec_phase_busy = c->ar.alloc<unsigned long long>(std::max<size_t>(1, c->dec_ph.size()));
+  c->d_blk_info = c->ar.alloc<int>(c->nblocks); C.blk_info = c->d_blk_info;
+  C.phase_busy = c->d_phase_busy; C.phase_first = c->d_phase_first; C.phase_last = c->d_phase_last; C.blk_busy = c->d_blk_busy; C.dec_phase_busy = c->d_dec_phase_busy;
   *out = c;
   return OFA_OK;
 }
@@ -808,8 +832,11 @@ extern "C" int ofa_launch(ofa_ctx* c, int nsteps) {
   C.step_done = c->d_step_done;
   C.step_base = c->steps_total;
   cudaMemsetAsync(c->d_status, 0, sizeof(DevStatus), c->stream);
-  cudaMemsetAsync(c->d_finished, 0, sizeof(int), c->stream);
+  cudaMemsetAsync(c->d_finished, 0, 2 * sizeof(int), c->stream);
+  C.arrived = c->d_finished + 1;
   cudaMemsetAsync(c->d_phase_busy, 0, sizeof(unsigned long long) * std::max<size_t>(1, c->train_ph.size()), c->stream);
+  cudaMemsetAsync(c->d_blk_busy, 0, sizeof(unsigned long long) * 2 * c->nblocks, c->stream);
+  cudaMemsetAsync(c->d_dec_phase_busy, 0, sizeof(unsigned long long) * std::max<size_t>(1, c->dec_ph.size()), c->stream);
   C.smem_bytes = c->smem;
   const Ctx& L = C;
   cudaEventRecord(c->ev0, c->stream);
@@ -877,6 +904,32 @@ extern "C" int ofa_phase_info(const ofa_ctx* c, int phase, char* name, size_t na
   if (kind) *kind = p.d.kind;
   if (ntasks) *ntasks = p.d.ntasks;
   if (busy_ns) { if (c->dry) *busy_ns = 0; else { cudaSetDevice(c->device); cudaMemcpy(busy_ns, c->d_phase_busy + phase, 8, cudaMemcpyDeviceToHost); } }
+  return OFA_OK;
+}
+extern "C" int ofa_read_block_busy(ofa_ctx* c, unsigned long long* out, size_t n) {
+  if (!c || !out || c->dry || n > (size_t)2 * c->nblocks) return fail(c, OFA_BAD_ARGUMENT, "bad request");
+  if (c->in_flight) return fail(c, OFA_BAD_ARGUMENT, "launch in flight");
+  cudaSetDevice(c->device);
+  return cudaMemcpy(out, c->d_blk_busy, n * 8, cudaMemcpyDeviceToHost) == cudaSuccess ? OFA_OK : fail(c, OFA_CUDA_ERROR, "D2H failed");
+}
+extern "C" int ofa_read_decode_trace(ofa_ctx* c, unsigned long long* out, size_t n) {
+  if (!c || !out || c->dry || n > 64 || !c->cfg.use_decode) return fail(c, OFA_BAD_ARGUMENT, "bad request");
+  if (c->in_flight) return fail(c, OFA_BAD_ARGUMENT, "launch in flight");
+  cudaSetDevice(c->device);
+  return cudaMemcpy(out, c->C.dp.trace, n * 8, cudaMemcpyDeviceToHost) == cudaSuccess ? OFA_OK : fail(c, OFA_CUDA_ERROR, "D2H failed");
+}
+extern "C" int ofa_read_block_info(ofa_ctx* c, int* out, size_t n) {
+  if (!c || !out || c->dry || n > (size_t)c->nblocks) return fail(c, OFA_BAD_ARGUMENT, "bad request");
+  if (c->in_flight) return fail(c, OFA_BAD_ARGUMENT, "launch in flight");
+  cudaSetDevice(c->device);
+  return cudaMemcpy(out, c->d_blk_info, n * 4, cudaMemcpyDeviceToHost) == cudaSuccess ? OFA_OK : fail(c, OFA_CUDA_ERROR, "D2H failed");
+}
+extern "C" int ofa_decode_phase_info(const ofa_ctx* c, int phase, char* name, size_t name_cap, int* ntasks, unsigned long long* busy_ns) {
+  if (!c || phase < 0 || phase >= (int)c->dec_ph.size()) return OFA_BAD_ARGUMENT;
+  const HostPhase& p = c->dec_ph[phase];
+  if (name && name_cap) { strncpy(name, p.name.c_str(), name_cap - 1); name[name_cap - 1] = 0; }
+  if (ntasks) *ntasks = p.d.ntasks;
+  if (busy_ns) { if (c->dry) *busy_ns = 0; else { cudaSetDevice(c->device); cudaMemcpy(busy_ns, c->d_dec_phase_busy + phase, 8, cudaMemcpyDeviceToHost); } }
   return OFA_OK;
 }
 extern "C" int ofa_phase_deps(const ofa_ctx* c, int job, int phase, int* dep_phase, int* dep_delta, int cap) {

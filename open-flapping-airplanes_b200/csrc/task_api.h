@@ -103,19 +103,23 @@ struct DecodeState {       // device memory; fixed-point residual makes the task
   int* out_tokens;         // pinned ring [out_cap]
   int out_cap;
 };
-enum { DS_TOKEN = 0, DS_POS = 1, DS_STEP = 2, DS_CTXFULL = 3, DS_ASTEP = 4 };
+enum { DS_TOKEN = 0, DS_POS = 1, DS_STEP = 2, DS_CTXFULL = 3, DS_ASTEP = 4,
+       DS_POSKEY = 5,   // (context epoch << 16) | pos in ONE word: a prefetch made ahead of time can tell whether the rows it copied belong to the context the task finally runs in
+       DS_EPOCH = 6 };
 
 struct DecodeParams {
   // weights: pointers into the SAME working-copy buffer the trainer updates
   const void *wte, *wpe, *head, *gf;
   const void* const* wqkv; const void* const* wo; const void* const* wup; const void* const* wdn;
   const void* const* g1; const void* const* g2;   // device arrays [L]
+  const void *tm_qkv, *tm_up, *tm_wo;             // device arrays [L] of 128-byte TMA descriptors (unswizzled 2-D views of Wqkv, Wup, Wo) for the weight prefetch
   DecodeState st;
   float temperature;       // <= 0: greedy
   unsigned long long seed;
   const int* forced; int nforced;
   int auto_reset, answer_len;
   int max_steps;           // stop decoding after this many tokens (0 = until training finishes)
+  unsigned long long* trace;   // optional: 64 %globaltimer stamps of stage boundaries inside serving task 0 of layer 0
 };
 
 struct DevStatus;
@@ -128,6 +132,7 @@ struct Ctx {
   int* tok_in; int* tok_tgt;
   int step_base;            // steps completed by earlier launches: added to the step index for data windows, LR and AdamW
   unsigned long long *phase_busy, *phase_first, *phase_last; int prof_step;
+  unsigned long long* dec_phase_busy;   // per serving phase: summed task time (ns)
   unsigned long long* step_done; float* loss_hist; unsigned long long* blk_busy; int* finished; unsigned long long* t_end;
   int infer_sms, reserved_sms, train_sms, use_decode, use_train;
   const int* smid_rank;     // %smid -> dense SM rank (nullptr = identity)
@@ -135,6 +140,8 @@ struct Ctx {
   Live* live;
   DevStatus* status;
   unsigned long long dep_timeout_ns;
+  int* blk_info;            // per block: %smid | role << 16 (1 serve, 2 reserved-idle, 3 train, 4 idle)
+  int* arrived;             // blocks of this launch that have started (idle partitions leave only when all have)
   int smem_bytes;           // dynamic shared memory per block; its last 256 bytes hold barriers (tensor-core path) and the scheduler's hand-off words
 };
 

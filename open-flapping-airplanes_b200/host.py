@@ -151,6 +151,30 @@ class Megakernel:
             res.append({"name": name.value.decode(), "kind": kind.value, "ntasks": nt.value, "busy_ns": busy.value})
         return res
 
+    def block_busy_ns(self, nblocks=296):
+        out = np.zeros(2 * nblocks, dtype=np.uint64)
+        self._chk(self.lib.ofa_read_block_busy(self.h, out.ctypes.data_as(C.c_void_p), out.size))
+        return out.reshape(nblocks, 2)
+
+    def block_info(self, nblocks=296):
+        """(smid, role) per block of the last launch; role 1 serving, 2 reserved, 3 training, 4 idle"""
+        out = np.zeros(nblocks, dtype=np.int32)
+        self._chk(self.lib.ofa_read_block_info(self.h, out.ctypes.data_as(C.c_void_p), out.size))
+        return out & 0xFFFF, out >> 16
+
+    def decode_trace(self):
+        out = np.zeros(64, dtype=np.uint64)
+        self._chk(self.lib.ofa_read_decode_trace(self.h, out.ctypes.data_as(C.c_void_p), 64))
+        return out
+
+    def decode_phases(self):
+        res, i = [], 0
+        while True:
+            name = C.create_string_buffer(64); nt, busy = C.c_int(), C.c_ulonglong()
+            if self.lib.ofa_decode_phase_info(self.h, i, name, 64, C.byref(nt), C.byref(busy)) != capi.OK:
+                return res
+            res.append({"name": name.value.decode(), "ntasks": nt.value, "busy_ns": busy.value}); i += 1
+
     def phase_deps(self, phase, job=0):
         ph = (C.c_int * 64)(); de = (C.c_int * 64)()
         n = self.lib.ofa_phase_deps(self.h, job, phase, ph, de, 64)

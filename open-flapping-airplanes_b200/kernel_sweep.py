@@ -154,6 +154,26 @@ def run_decode(ofa, sms, ntok):
     mk.load_weights(rng.standard_normal(mk.num_params, dtype=np.float32) * np.float32(0.02))
     mk.run(64)
     ms = mk.run(ntok)
+    if os.environ.get("OFA_SWEEP_VERBOSE"):
+        bb = mk.block_busy_ns()[:, 1]
+        act = bb[bb > 0]
+        smid, role = mk.block_info()
+        print("  blocks per role (1 serve, 2 reserved, 3 train, 4 idle):", {int(r): int((role == r).sum()) for r in np.unique(role)}, file=sys.stderr)
+        print("  serve blocks: ids", np.nonzero(role == 1)[0].tolist(), "smids", smid[role == 1].tolist(), file=sys.stderr)
+        cnt = np.bincount(smid, minlength=160)
+        print("  smids with 3 blocks:", np.nonzero(cnt == 3)[0].tolist(), file=sys.stderr)
+        print("  smid of blocks 272..295:", smid[272:].tolist(), "roles", role[272:].tolist(), file=sys.stderr)
+        print("  smid of blocks 148..171:", smid[148:172].tolist(), file=sys.stderr)
+        print("  smid of blocks 0..23:", smid[0:24].tolist(), file=sys.stderr)
+        print("  blocks per smid histogram:", np.bincount(np.bincount(smid, minlength=160)).tolist(), " max smid", int(smid.max()), file=sys.stderr)
+        print(f"  serving blocks that ran tasks: {act.size}, mean busy {act.mean() / 1e6:.2f} ms of {ms:.2f} ms, min {act.min() / 1e6:.2f} max {act.max() / 1e6:.2f}", file=sys.stderr)
+        tr = mk.decode_trace().astype(np.int64)
+        print("  qkv task stages (us): issue+prefetch %.2f, LN prologue %.2f, gemv %.2f, store %.2f | scheduler view: start->task %.2f, task end->signal %.2f" % (
+            (tr[1] - tr[0]) / 1e3, (tr[2] - tr[1]) / 1e3, (tr[3] - tr[2]) / 1e3, (tr[4] - tr[3]) / 1e3, (tr[0] - tr[16]) / 1e3, (tr[17] - tr[4]) / 1e3), file=sys.stderr)
+        print("  up+down task stages (us): issue+prefetch %.2f, LN prologue %.2f, up gemv %.2f, gelu+down %.2f | start->task %.2f, end->signal %.2f" % (
+            (tr[9] - tr[8]) / 1e3, (tr[10] - tr[9]) / 1e3, (tr[11] - tr[10]) / 1e3, (tr[12] - tr[11]) / 1e3, (tr[8] - tr[18]) / 1e3, (tr[19] - tr[12]) / 1e3), file=sys.stderr)
+        for p in mk.decode_phases()[:3] + mk.decode_phases()[-2:]:
+            print(f"  {p['name']:20s} tasks {p['ntasks']:4d}  mean task {p['busy_ns'] / 1e3 / max(1, p['ntasks']) / ntok:7.2f} us", file=sys.stderr)
     mk.close()
     by = 2.0 * (12 * 12 * D * D + V * D) + 36864.0 * 131      # weights + KV at the mean position of a 261-step answer cycle
     return {"kernel": f"decode_{sms}sm", "shape": [sms], "ms": ms / ntok, "tok_s": ntok / ms * 1e3, "gbs": by / (ms / ntok) / 1e6, "bound": "hbm", "algorithmic_bytes": by}
