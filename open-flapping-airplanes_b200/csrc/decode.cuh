@@ -116,6 +116,13 @@ template <class T, int D, int DH> struct Smem {
   }
 };
 
+// once per serving block, before its first task
+template <class T, int D, int DH>
+__device__ __forceinline__ void block_init(unsigned char* smem, int Tctx) {
+  Smem<T, D, DH> S(smem, Tctx);
+  if (threadIdx.x < 4) S.meta[threadIdx.x] = 0;
+}
+
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
@@ -255,6 +262,7 @@ __device__ __forceinline__ void task_qkv(const DecodeParams& P, const ModelDims&
   const DecodeState& st = P.st;
   const bool tr = layer == 0 && t == 0;
   trace(P.trace, tr, 0);
+  if (threadIdx.x == 0) S.meta[2] = 0;                 // xs no longer holds a final-LayerNorm row
   prologue_ln<T, D>(st.xw, reinterpret_cast<const T*>(P.g1[layer]), S.xs, S.scratch, t == 0 ? st.xr : nullptr);
   trace(P.trace, tr, 1);
   OFA_DEC_WAIT_FILL();
@@ -286,6 +294,7 @@ __device__ __forceinline__ void task_attwo(const DecodeParams& P, const ModelDim
   const int tid = threadIdx.x, g = tid / LPK, l = tid % LPK;
   const int head = t / G::NCB, cb = t % G::NCB;
   const int pos = __ldcg(&st.scal[DS_POS]), n = pos + 1;
+  if (tid == 0) S.meta[2] = 0;
   if (tid < DH) qs[tid] = ldcg_f<T>(reinterpret_cast<const T*>(st.q) + head * DH + tid) * rsqrtf((float)DH);
   OFA_DEC_WAIT_FILL();
   const int nres = (S.meta[1] == (__ldcg(&st.scal[DS_POSKEY]) >> 16)) ? min(S.meta[0], pos) : 0;   // rows valid in shared memory
@@ -375,6 +384,7 @@ __device__ __forceinline__ void task_updn(const DecodeParams& P, const ModelDims
   const DecodeState& st = P.st;
   const bool tr = layer == 0 && t == 0;
   trace(P.trace, tr, 8);
+  if (threadIdx.x == 0) S.meta[2] = 0;
   prologue_ln<T, D>(st.xr, reinterpret_cast<const T*>(P.g2[layer]), S.xs, S.scratch, nullptr);
   trace(P.trace, tr, 9);
   OFA_DEC_WAIT_FILL();
@@ -401,7 +411,12 @@ __device__ __forceinline__ void task_head(const DecodeParams& P, const ModelDims
   Smem<T, D, DH> S(smem, md.T);
   const DecodeState& st = P.st;
   const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31, layer = -1;
-  prologue_ln<T, D>(st.xw, reinterpret_cast<const T*>(P.gf), S.xs, S.scratch, nullptr);
+  // the final LayerNorm is the same for every head task of a token: a block that runs several of them in a row keeps it
+  const int tag = __ldcg(&st.scal[DS_STEP]) + 1;
+  if (S.meta[2] != tag) {
+    prologue_ln<T, D>(st.xw, reinterpret_cast<const T*>(P.gf), S.xs, S.scratch, nullptr);
+    if (tid == 0) S.meta[2] = tag;
+  }
   OFA_DEC_WAIT_FILL();
   const T* Wh = reinterpret_cast<const T*>(S.w);
 #pragma unroll 2
@@ -436,7 +451,8 @@ __device__ __forceinline__ void task_head(const DecodeParams& P, const ModelDims
     if (gi < md.valid_vocab) { v0 = l; v1 = temp > 0.f ? l * invT + gumbel(P.seed, step, gi) : l; }
   }
   float b0 = v0; int i0 = gi; block_argmax(b0, i0, sv, si);
-  float b1 = v1; int i1 = gi; block_argmax(b1, i1, sv, si);
+  float b1 = b0; int i1 = i0;
+  if (temp > 0.f) { b1 = v1; i1 = gi; block_argmax(b1, i1, sv, si); }
   if (tid == 0) { st.cand_v[t] = b0; st.cand_i[t] = i0; st.cand_v[nchunk + t] = b1; st.cand_i[nchunk + t] = i1; }
 }
 #undef OFA_DEC_WAIT_FILL

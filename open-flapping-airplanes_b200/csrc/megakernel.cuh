@@ -183,6 +183,7 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
   uint32_t fills = 0;
   if (job_id == 1) {
     if (tid == 0) { mbar_init(fill_bar, 1); mbar_fence_init(); }
+    dec::block_init<T, D, DH>(smem, C.md.T);
     __syncthreads();
   }
   for (;;) {
@@ -234,9 +235,9 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
     if (job_id == 0) run_train_task<T, D, DH>(C, d, ph, local, step, smem, gp);
     else run_decode_task<T, D, DH>(C, d, local, smem, fill_bar, fills & 1u);
     if (filled) fills++;
-    __threadfence();
     __syncthreads();
     if (tid == 0) {
+      __threadfence();       // after the block barrier: orders every thread's writes of this task before the completion signal
       const u64 t1 = gtimer();
       if (job_id == 1 && C.dp.trace && local == 0 && (ph == 0 || ph == 2)) C.dp.trace[17 + ph] = t1;
       busy += t1 - t0;
