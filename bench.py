@@ -267,6 +267,14 @@ def main():
             bb = mk.block_busy_ns()
             print(f"  blocks that ran training tasks: {(bb[:, 0] > 0).sum()}, serving tasks: {(bb[:, 1] > 0).sum()}; mean training-block busy {bb[:, 0][bb[:, 0] > 0].mean() / 1e6 / K:.3f} ms/step", file=sys.stderr)
             tot = sum(p["busy_ns"] for p in mk.phases()) or 1
+            import re
+            cat = {}
+            for p in mk.phases():
+                key = re.sub(r"^L\d+ ", "L* ", p["name"]); key = re.sub(r"adamw L\d+", "adamw L*", key)
+                c = cat.setdefault(key, [0, 0]); c[0] += p["busy_ns"]; c[1] += p["ntasks"]
+            print("  per category (block-ms per step, share of busy, mean us per task):", file=sys.stderr)
+            for k, (b, n) in sorted(cat.items(), key=lambda kv: -kv[1][0]):
+                print(f"    {k:22s} {b / 1e6 / K:8.3f}  {100.0 * b / tot:5.1f} %  {b / 1e3 / K / max(1, n):8.2f} us/task  ({n} tasks)", file=sys.stderr)
             for p in sorted(mk.phases(), key=lambda p: -p["busy_ns"])[:40]:
                 print(f"  {p['name']:24s} tasks {p['ntasks']:6d}  busy {p['busy_ns'] / 1e6 / K:8.3f} ms/step  {100.0 * p['busy_ns'] / tot:5.1f} %", file=sys.stderr)
         if world == 1 and not args.no_cpu_baseline:

@@ -175,11 +175,11 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
   u64 busy = 0;
   int rstep = -1, rph = -1;                         // thread 0: the (step, phase) last seen ready
   const unsigned total = (unsigned)J.nsteps * (unsigned)J.tasks_per_step;
-  gemm_tc::GemmPipe gp; gp.stage_count = gp.tile_count = gp.tmem_base = 0;
+  gemm_tc::GemmPipe gp; gp.stage_count[0] = gp.stage_count[1] = gp.tile_count[0] = gp.tile_count[1] = gp.tmem_base = 0;
   const bool use_tc = IsBf16<T>::value && job_id == 0;
   if (use_tc) gemm_tc::block_init(gp, smem, C.status);
   // serving blocks: one mbarrier counts the bytes of the weight prefetch of the task they hold a ticket for
-  const uint32_t fill_bar = smem_u32(smem + C.smem_bytes - 256 + 96);
+  const uint32_t fill_bar = smem_u32(smem + C.smem_bytes - 256 + 96);   // see the control-area map in gemm_tc.cuh
   uint32_t fills = 0;
   if (job_id == 1) {
     if (tid == 0) { mbar_init(fill_bar, 1); mbar_fence_init(); }

@@ -109,9 +109,26 @@ bool prepare_gemm_bf16(PhaseDesc& d, Arena& ar, int nsub_cfg, int nblocks, std::
     return false;
   }
   if ((d.epi == GE_RES || d.epi == GE_GELU || d.epi == GE_DGELU) && !g.aux) { err = "GEMM epilogue needs aux"; return false; }
-  const int tm = g.M / 128, tn = g.N / 128;
+  // nsub_cfg: n = strips of n tiles (0 = automatic); 2000 + n = the same with 256-wide tiles where N allows. 256-wide tiles are
+  // opt-in: with two 48 KB stages per block they measured slower than three 32 KB stages of the 128-wide tile on every model
+  // shape except lm_head dW (960 vs 702 TFLOP/s), i.e. the main loop is bound by bytes in flight, not by operand traffic alone.
+  const bool want256 = nsub_cfg >= 2000;
+  if (want256) nsub_cfg -= 2000;
+  g.bn = (want256 && g.N % 256 == 0) ? 256 : 128;
+  const int tm = g.M / 128, tn = g.N / g.bn;
   int nsub = nsub_cfg;
-  if (nsub <= 0) { nsub = 1; for (int c = 4; c >= 2; c--) if ((long)tm * ((tn + c - 1) / c) >= 2L * nblocks) { nsub = c; break; } }
+  if (nsub <= 0) {
+    // strip length: fewest waves of the resident blocks, then the most tasks (a strip pays pipeline fill, drain and the claim once)
+    const int kt = g.K / 64;
+    double best = 1e30; nsub = 1;
+    for (int c = 1; c <= std::min(tn, 8); c++) {
+      const long tasks = (long)tm * ((tn + c - 1) / c);
+      const long waves = (tasks + nblocks - 1) / nblocks;
+      const double per_k = g.bn == 256 ? 0.9 : 0.66;           // us per 64-deep K step of one block with the GPU busy (measured)
+      const double cost = waves * (5.0 + c * kt * per_k);
+      if (cost < best - 1e-9) { best = cost; nsub = c; }
+    }
+  }
   nsub = std::max(1, std::min(nsub, tn));
   g.nsub = nsub;
   d.tiles_m = tm;

@@ -53,7 +53,8 @@ struct GemmArgs {
   int M, N, K;
   int lda, ldb, ldc, ldaux;   // leading dimensions in elements
   int accumulate;             // GE_F32 only
-  int nsub;                   // consecutive 128-wide N tiles handled by one task (tensor-core path)
+  int nsub;                   // consecutive N tiles handled by one task (tensor-core path)
+  int bn;                     // tile width of the tensor-core path: 256 when N is a multiple of 256, else 128
   const void* tmA;            // device pointers to the two TMA descriptors (tensor-core path), 64-byte aligned
   const void* tmB;
 };

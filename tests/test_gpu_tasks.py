@@ -153,7 +153,7 @@ GEMM_CASES = [  # (layout, epi, M, N, K)
 
 
 @pytest.mark.parametrize("layout,epi,M,N,Kd", GEMM_CASES)
-@pytest.mark.parametrize("nsub", [1, 3])
+@pytest.mark.parametrize("nsub", [1, 3, 2002])      # 2002: 256-wide tiles (where N allows) in strips of 2
 def test_gemm_tensor_core(ofa, K, oracle, layout, epi, M, N, Kd, nsub):
     g = torch.Generator().manual_seed(10 + layout * 7 + epi)
     ashape = (M, Kd) if layout != 2 else (Kd, M)
