@@ -265,6 +265,9 @@ def main():
         }
         if args.phase_table:
             bb = mk.block_busy_ns()
+            bw = mk.block_wait_ns()
+            act = bb[:, 0] > 0
+            print(f"  per training block, ms/step: dependency wait {bw[0][act].mean() / 1e6 / K:.3f}, claim {bw[1][act].mean() / 1e6 / K:.3f}, hand-off {bw[2][act].mean() / 1e6 / K:.3f}, signalling {bw[3][act].mean() / 1e6 / K:.3f}; tasks per step {sum(p['ntasks'] for p in mk.phases())}", file=sys.stderr)
             print(f"  blocks that ran training tasks: {(bb[:, 0] > 0).sum()}, serving tasks: {(bb[:, 1] > 0).sum()}; mean training-block busy {bb[:, 0][bb[:, 0] > 0].mean() / 1e6 / K:.3f} ms/step", file=sys.stderr)
             tot = sum(p["busy_ns"] for p in mk.phases()) or 1
             import re

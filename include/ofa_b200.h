@@ -61,6 +61,8 @@ typedef struct {
   int grad_bf16;            /* weight gradients are written as bf16 (the all-reduce bucket format)                */
   int ext_sync;             /* 1: gradients are cut into buckets; the graph raises a "ready" flag per bucket and holds the bucket's AdamW until the matching "done" flag is raised from outside (the all-reduce) */
   int bucket_bytes;         /* target bucket size for ext_sync (0 = 25 MiB)                                       */
+  int adam_interleave;      /* 1: place each layer's AdamW phase inside the backward pass (experimental, default 0)     */
+  int head_dx_splitk;       /* 1: compute lm_head dX as K-split partial products + reduce (experimental, default 0)     */
   int gemm_nsub;            /* consecutive 128-wide N tiles per GEMM task (0 = default)                           */
   double timeout_s;         /* device-side bound for any dependency wait (0 = default 20 s)                       */
   int device;               /* CUDA device ordinal; < 0 = planning context: layout, buckets and phase graphs are built and can be queried, nothing touches a device and nothing can be launched */
@@ -110,7 +112,7 @@ int ofa_read_losses(ofa_ctx* ctx, float* out, size_t n);                  /* los
 int ofa_read_step_times(ofa_ctx* ctx, unsigned long long* out, size_t n); /* %globaltimer ns at the end of each step of the last launch */
 int ofa_num_phases(const ofa_ctx* ctx);
 int ofa_phase_info(const ofa_ctx* ctx, int phase, char* name, size_t name_cap, int* kind, int* ntasks, unsigned long long* busy_ns);
-/* busy nanoseconds of every block in the last launch: out[2*block + job] (job 0 training, 1 serving), n <= 2 * grid size (ofa.cu:313 blk_busy) */
+/* busy nanoseconds of every block in the last launch: out[2*block + job] (job 0 training, 1 serving) for the first 2*grid entries (ofa.cu:313 blk_busy), then four rows of grid entries each: time the block's scheduler thread spent waiting for training dependencies, claiming tickets, handing the task to the block, and signalling completion; n <= 6 * grid size */
 int ofa_read_block_busy(ofa_ctx* ctx, unsigned long long* out, size_t n);
 /* in-kernel trace of the serving job (the reference's DTRACE, decode_wide.cuh:11-16): %globaltimer stamps of the stage boundaries inside task 0 of layer 0 (slots 0-4 QKV, 8-12 UP+DOWN, 16-19 scheduler-side start/end of those tasks), last token of the last launch */
 int ofa_read_decode_trace(ofa_ctx* ctx, unsigned long long* out, size_t n);

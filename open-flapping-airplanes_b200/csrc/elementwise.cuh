@@ -22,6 +22,7 @@ constexpr int CE_ROWS = 4;           // rows per cross-entropy task
 constexpr int EMB_VCHUNK = 128;      // vocabulary rows per embedding-backward task
 constexpr int OPT_CHUNK = 65536;     // elements per AdamW task
 constexpr int WPE_ROWS = 4;          // positions per wpe-backward task
+constexpr int SUM_CHUNK = 16384;     // elements per split-K reduce task
 
 __device__ __forceinline__ void ld4(const float* p, float* f) { ldv(p, f); }
 __device__ __forceinline__ void ld4(const bf16* p, float* f) {
@@ -416,6 +417,24 @@ __device__ __forceinline__ void adamw_task(int task, float* W, const GT* G, floa
       w[k] = p - step_size * (m[k] / denom);
     }
     st4(W + i, w); st4(M + i, m); st4(Vv + i, v); st4(Wact + i, w);
+  }
+}
+
+// out[i] = T(part0[i] + part1[i] + ...) in index order: the reduce of a split-K GEMM. Task = 16,384 elements (n % 8 == 0).
+template <class T>
+__device__ __forceinline__ void sumcast_task(int task, T* out, void* const* parts, int nparts, size_t n) {
+  const size_t s0 = (size_t)task * SUM_CHUNK, e0 = s0 + SUM_CHUNK < n ? s0 + SUM_CHUNK : n;
+  for (size_t i = s0 + (size_t)threadIdx.x * 8; i < e0; i += NTHR * 8) {
+    float acc[8];
+#pragma unroll
+    for (int k = 0; k < 8; k++) acc[k] = 0.f;
+    for (int p = 0; p < nparts; p++) {
+      const float* src = reinterpret_cast<const float*>(parts[p]) + i;
+      const float4 a = *reinterpret_cast<const float4*>(src), b = *reinterpret_cast<const float4*>(src + 4);
+      acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w; acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+    }
+#pragma unroll
+    for (int k = 0; k < 8; k++) out[i + k] = from_f<T>(acc[k]);
   }
 }
 

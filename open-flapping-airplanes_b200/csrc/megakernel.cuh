@@ -112,6 +112,9 @@ __device__ __forceinline__ void run_train_task(const Ctx& C, const PhaseDesc& d,
       else ew::adamw_task<T, float>(local, (float*)d.p[0], (const float*)d.p[1], (float*)d.p[2], (float*)d.p[3], (T*)d.p[4], d.n, hp, (const int2*)d.p[5], d.i0);
       break;
     }
+    case TK_SUMCAST:
+      ew::sumcast_task<T>(local, (T*)d.p[0], &d.p[1], d.i0, d.n);
+      break;
     case TK_EXT_SIGNAL:
       // flag values count steps since the context was created, so a stale value from an earlier launch is always too small
       if (threadIdx.x == 0) { __threadfence_system(); *reinterpret_cast<volatile int*>(d.p[0]) = C.step_base + step + 1; __threadfence_system(); }
@@ -170,7 +173,11 @@ __device__ __forceinline__ int wait_deps(const Ctx& C, const Job& J, int job_id,
 
 template <class T, int D, int DH>
 __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* smem) {
-  volatile int* s_sel = reinterpret_cast<volatile int*>(smem + C.smem_bytes - 128);   // the last 256 bytes of dynamic shared memory are the block's control area
+  unsigned char* ctrl = smem + C.smem_bytes - 512;   // the last 512 bytes of dynamic shared memory are the block's control area (map in gemm_tc.cuh)
+  volatile int* s_sel = reinterpret_cast<volatile int*>(ctrl + 128);
+  PhaseDesc* s_desc = reinterpret_cast<PhaseDesc*>(ctrl + 256);
+  static_assert(sizeof(PhaseDesc) <= 256, "descriptor copy does not fit the control area");
+  int cached_ph = -1;
   const int tid = threadIdx.x;
   u64 busy = 0;
   int rstep = -1, rph = -1;                         // thread 0: the (step, phase) last seen ready
@@ -179,39 +186,64 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
   const bool use_tc = IsBf16<T>::value && job_id == 0;
   if (use_tc) gemm_tc::block_init(gp, smem, C.status);
   // serving blocks: one mbarrier counts the bytes of the weight prefetch of the task they hold a ticket for
-  const uint32_t fill_bar = smem_u32(smem + C.smem_bytes - 256 + 96);   // see the control-area map in gemm_tc.cuh
+  const uint32_t fill_bar = smem_u32(ctrl + 96);
   uint32_t fills = 0;
   if (job_id == 1) {
     if (tid == 0) { mbar_init(fill_bar, 1); mbar_fence_init(); }
     dec::block_init<T, D, DH>(smem, C.md.T);
     __syncthreads();
   }
+  u64 waited = 0, t_claim = 0, t_sync = 0, t_tail = 0, tl0 = 0, tl1 = 0;   // thread 0: where the time outside tasks goes
+  int c_ph = 0, c_lo = 0, c_hi = 0;                  // thread 0: cached phase and its ticket range [c_lo, c_hi) within a step
+  unsigned next_g = 0; bool have_next = false; unsigned claims = 0;   // thread 0: the ticket taken at the end of the previous task
+  if (tid == 0) c_hi = __ldg(J.prefix + 1);
   for (;;) {
     if (tid == 0) {                                  // ---- claim (and, for the training job, wait for the dependencies)
+      tl0 = gtimer(); if (tl1) t_tail += tl0 - tl1;
+      const u64 w_before = waited;
       int res = 0, step = 0, ph = 0, local = 0;
-      if (aborted(C.status) || (job_id == 1 && C.use_train && ld_relaxed(C.finished))) res = -2;
+      // the abort / finished words are looked at inside every wait loop; here only now and then, a claim should not pay for them
+      if ((claims++ & 15u) == 0 && (aborted(C.status) || (job_id == 1 && C.use_train && ld_relaxed(C.finished)))) res = -2;
       else {
-        const unsigned g = atomicAdd(J.ticket, 1u);
+        const unsigned g = have_next ? next_g : atomicAdd(J.ticket, 1u);
+        have_next = false;
         if (g >= total) res = -2;
         else {
           step = (int)(g / (unsigned)J.tasks_per_step);
           const int r = (int)(g - (unsigned)step * (unsigned)J.tasks_per_step);
-          int lo = 0, hi = J.nph;                   // last phase whose prefix <= r
-          while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if (__ldg(J.prefix + mid) <= r) lo = mid; else hi = mid; }
-          ph = lo; local = r - __ldg(J.prefix + ph);
+          // tickets of a block mostly stay in the phase of its previous ticket or move a few phases on: keep that phase's
+          // bounds in registers and walk forward; fall back to a binary search only when the ticket lies before them
+          if (r < c_lo) {
+            int lo = 0, hi = J.nph;                 // last phase whose prefix <= r
+            while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if (__ldg(J.prefix + mid) <= r) lo = mid; else hi = mid; }
+            c_ph = lo; c_lo = __ldg(J.prefix + lo); c_hi = __ldg(J.prefix + lo + 1);
+          }
+          while (r >= c_hi) { c_ph++; c_lo = c_hi; c_hi = __ldg(J.prefix + c_ph + 1); }
+          ph = c_ph; local = r - c_lo;
           if (job_id == 0 && !(step == rstep && ph == rph)) {
+            const u64 w0 = gtimer();
             res = wait_deps(C, J, job_id, step, ph, local);
+            waited += gtimer() - w0;
             if (res == 0) { rstep = step; rph = ph; }
           }
         }
       }
       s_sel[0] = res; s_sel[1] = step; s_sel[2] = ph; s_sel[3] = local;
+      tl1 = gtimer(); t_claim += (tl1 - tl0) - (waited - w_before);
     }
     __syncthreads();
     int res = s_sel[0];
     const int step = s_sel[1], ph = s_sel[2], local = s_sel[3];
     if (res < 0) break;
-    const PhaseDesc& d = J.ph[ph];
+    // The descriptor is fetched once per phase change with one coalesced load and then read from shared memory: every
+    // dependency check ends with a device-scope acquire, after which L1 no longer holds it, and the chain of dependent global
+    // loads that decoding it would take was a measurable part of the per-task overhead.
+    if (ph != cached_ph) {
+      if (tid < (int)(sizeof(PhaseDesc) / 4)) reinterpret_cast<uint32_t*>(s_desc)[tid] = __ldg(reinterpret_cast<const uint32_t*>(J.ph + ph) + tid);
+      cached_ph = ph;
+      __syncthreads();
+    }
+    const PhaseDesc& d = *s_desc;
     bool filled = false;
     if (job_id == 1) {                               // ---- serving: start the weight prefetch, THEN wait for the dependencies
       filled = dec::prefetch<T, D, DH>(C.dp, C.md, d.kind, d.i0, local, smem, fill_bar);
@@ -231,14 +263,21 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
       __syncthreads();                               // s_sel may be rewritten by thread 0 only after everyone has read it
     }
     u64 t0 = 0;
-    if (tid == 0) { t0 = gtimer(); if (job_id == 1 && C.dp.trace && local == 0 && (ph == 0 || ph == 2)) C.dp.trace[16 + ph] = t0; }
+    if (tid == 0) { t0 = gtimer(); t_sync += t0 - tl1; if (job_id == 1 && C.dp.trace && local == 0 && (ph == 0 || ph == 2)) C.dp.trace[16 + ph] = t0; }
     if (job_id == 0) run_train_task<T, D, DH>(C, d, ph, local, step, smem, gp);
     else run_decode_task<T, D, DH>(C, d, local, smem, fill_bar, fills & 1u);
     if (filled) fills++;
     __syncthreads();
     if (tid == 0) {
-      __threadfence();       // after the block barrier: orders every thread's writes of this task before the completion signal
-      const u64 t1 = gtimer();
+      // Completion signal first: a release at device scope after the block barrier orders every thread's writes of this task
+      // before it (no separate fence, and nobody waits for its round trip). The step's last phase needs the old value.
+      int old = -1;
+      if (ph == J.last_phase) { __threadfence(); old = atomicAdd(J.done + ph, 1); }
+      else red_release_add(J.done + ph, 1);
+      // Then take the next ticket: its round trip overlaps the bookkeeping below and the block hand-off. The task is finished,
+      // so holding the next ticket cannot delay anything this block still has to do (every dependency is a lower ticket).
+      next_g = atomicAdd(J.ticket, 1u); have_next = true;
+      const u64 t1 = gtimer(); tl1 = t1;
       if (job_id == 1 && C.dp.trace && local == 0 && (ph == 0 || ph == 2)) C.dp.trace[17 + ph] = t1;
       busy += t1 - t0;
       if (job_id == 0 && C.phase_busy) {
@@ -246,9 +285,6 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
         if (step == C.prof_step) { atomicMin(C.phase_first + ph, t0); atomicMax(C.phase_last + ph, t1); }
       }
       if (job_id == 1 && C.dec_phase_busy) atomicAdd(C.dec_phase_busy + ph, t1 - t0);
-      int old = -1;
-      if (ph == J.last_phase) old = atomicAdd(J.done + ph, 1);
-      else red_release_add(J.done + ph, 1);            // no return value needed: do not wait for the round trip
       if (ph == J.last_phase && old == __ldg(J.ntasks + ph) * (step + 1) - 1) {     // last task of the step
         if (job_id == 0) {
           C.step_done[step] = t1;
@@ -259,7 +295,7 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
     }
   }
   if (use_tc) gemm_tc::block_exit(gp, smem, C.status);
-  if (tid == 0 && C.blk_busy) C.blk_busy[blockIdx.x * 2 + job_id] = busy;
+  if (tid == 0 && C.blk_busy) { C.blk_busy[blockIdx.x * 2 + job_id] = busy; if (job_id == 0 && C.blk_wait) { C.blk_wait[blockIdx.x] = waited; C.blk_wait[gridDim.x + blockIdx.x] = t_claim; C.blk_wait[2 * gridDim.x + blockIdx.x] = t_sync; C.blk_wait[3 * gridDim.x + blockIdx.x] = t_tail; } }
 }
 
 // A block of an idle partition must not leave before the whole grid has been placed: the hardware refills the slot of an

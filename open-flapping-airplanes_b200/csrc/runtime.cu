@@ -203,7 +203,7 @@ int smem_for(bool bf, int Tctx, int N) {
   m = std::max(m, ew::ln_bwd_smem_bytes<64>());
   m = std::max(m, dec::smem_bytes<float, 64, 16>(Tctx));
   m = std::max(m, (size_t)64 + 4096);
-  return (int)((m + 1023) / 1024 * 1024) + 256;   // + control area
+  return (int)((m + 1023) / 1024 * 1024) + 512;   // + control area
 }
 
 }  // namespace
@@ -361,7 +361,7 @@ bool build_train_graph(ofa_ctx* c) {
     end_deps = {"logits"};
   } else {
     { PhaseDesc d = mk(TK_CE, (int)((N + ew::CE_ROWS - 1) / ew::CE_ROWS)); d.p[0] = logits; d.p[1] = c->C.tok_tgt; d.p[2] = lossv;
-      const size_t usable = (size_t)((bf ? gemm_tc::BAR_OFFSET : c->smem - 256) - 64);
+      const size_t usable = (size_t)((bf ? gemm_tc::BAR_OFFSET : c->smem - 512) - 64);
       d.i0 = (int)(std::min(usable, V * sizeof(T)) / 16 * 16);
       addp("cross-entropy", d, {"logits", "data"}, {}); }
     { PhaseDesc d = mk(TK_CE_MEAN, 1); d.p[0] = meanloss; d.p[1] = lossv; addp("loss mean", d, {"cross-entropy"}, {}); }
@@ -394,8 +394,58 @@ bool build_train_graph(ofa_ctx* c) {
       addp("grads ready " + std::to_string(bi), d, buckets[bi].producers, {});
     };
 
+    // ---- optimizer helpers. Optionally (cfg.adam_interleave, and only without external gradient synchronisation) a layer's
+    // AdamW is placed INSIDE the backward pass, one layer below the one it updates, instead of after it. Off by default: on the
+    // full model it measured 0.5-0.9 % slower per step (the memory-bound tasks delay the chain of small backward phases).
+    auto gate = [&](const std::string& adam_name, std::vector<std::string> deps) {
+      if (!ext) return deps;
+      for (size_t bi = 0; bi < buckets.size(); bi++) for (const std::string& a : buckets[bi].adam_phases) if (a == adam_name) return std::vector<std::string>{"allreduce done " + std::to_string(bi)};
+      return deps;
+    };
+    auto mkadam = [&](size_t off, size_t n, const std::vector<Span>& nodecay) {
+      PhaseDesc d = mk(TK_ADAMW, (int)((n + ew::OPT_CHUNK - 1) / ew::OPT_CHUNK));
+      d.p[0] = c->W32 + off; d.p[1] = G(off); d.p[2] = c->M32 + off; d.p[3] = c->V32 + off; d.p[4] = Wact + off;
+      d.n = n; d.i0 = (int)nodecay.size(); d.i1 = gbf ? 1 : 0;
+      std::vector<int2> nd; for (const Span& sp : nodecay) nd.push_back(make_int2((int)(sp.off - off), (int)(sp.off - off + sp.n)));
+      int2* dn = c->ar.alloc<int2>(std::max<size_t>(1, nd.size()));
+      if (dn && !nd.empty()) c->ar.h2d(dn, nd.data(), nd.size() * sizeof(int2));
+      d.p[5] = dn;
+      return d;
+    };
+    auto emit_adam_head = [&]() { addp("adamw head", mkadam(lay.head, V * D, {}), gate("adamw head", {"head dW", "head dX"}), {}); };
+    auto emit_adam_layer = [&](int l) {
+      const std::string s = "L" + std::to_string(l) + " ";
+      const size_t off = lay.g1[l], end = (l + 1 < L) ? lay.g1[l + 1] : lay.gf + D;
+      std::vector<Span> nd = {Span{lay.g1[l], D}, Span{lay.g2[l], D}};
+      std::vector<std::string> deps = {s + "dWdown", s + "dWup", s + "dgamma2", s + "dWo", s + "dWqkv", s + "dgamma1", s + "ln1 bwd"};
+      if (l == L - 1) { nd.push_back(Span{lay.gf, D}); deps.push_back("lnf dgamma"); }
+      addp("adamw L" + std::to_string(l), mkadam(off, end - off, nd), gate("adamw L" + std::to_string(l), deps), {});
+    };
+    const bool interleave_adam = train && !ext && cfg.adam_interleave;
+
     // ---- backward
-    addp("head dX", mkgemm(GL_NN, GE_STORE, logits, V, Wact + lay.head, D, dxf, D, nullptr, 0, N, D, V, 0), {"cross-entropy"}, {});
+    {
+      // head dX has K = V: 192 tiles with a very long main loop (0.39 ms per tile). Optionally (cfg.head_dx_splitk) it is cut into
+      // S partial products over disjoint K ranges (fp32 partials, fixed summation order). Off by default: on the full model
+      // it measured 1.2 % slower per step, the long tiles run beside head dW and are not what the step waits for.
+      int S = 1;
+      if (bf && V >= 8192 && cfg.head_dx_splitk) for (int c = 4; c >= 2; c--) if (V % (64 * (size_t)c) == 0) { S = c; break; }
+      if (S == 1) addp("head dX", mkgemm(GL_NN, GE_STORE, logits, V, Wact + lay.head, D, dxf, D, nullptr, 0, N, D, V, 0), {"cross-entropy"}, {});
+      else {
+        const size_t Ks = V / S;
+        std::vector<std::string> parts;
+        PhaseDesc dsum = mk(TK_SUMCAST, (int)((N * D + ew::SUM_CHUNK - 1) / ew::SUM_CHUNK)); dsum.p[0] = dxf; dsum.i0 = S; dsum.n = N * D;
+        for (int k = 0; k < S; k++) {
+          float* part = abuf<float>(c, "dxf_part" + std::to_string(k), N * D);
+          dsum.p[1 + k] = part;
+          const std::string nm = "head dX k" + std::to_string(k);
+          addp(nm, mkgemm(GL_NN, GE_F32, logits + k * Ks, V, Wact + lay.head + k * Ks * D, D, part, D, nullptr, 0, N, D, (int)Ks, 0), {"cross-entropy"}, {});
+          parts.push_back(nm);
+        }
+        if (!c->ar.ok) { c->err = "out of device memory (split-K partials)"; return false; }
+        addp("head dX", dsum, parts, {});
+      }
+    }
     addp("head dW", mkgemm(GL_TN, wepi, logits, V, lnf, D, G(lay.head), D, nullptr, 0, V, D, N, 0), {"cross-entropy"}, {});
     if (ext && !lay.tied) signal(0);
     { PhaseDesc d = mk(TK_LN_BWD, rows16); d.p[0] = dxs[L]; d.p[1] = dgpf; d.p[2] = dxf; d.p[3] = xs[L]; d.p[4] = meanf; d.p[5] = rstdf; d.p[6] = Wact + lay.gf; d.p[7] = nullptr;
@@ -408,6 +458,7 @@ bool build_train_graph(ofa_ctx* c) {
       const std::string s = "L" + std::to_string(l) + " ";
       addp(s + "dpre", mkgemm(GL_NT, GE_DGELU, dxs[l + 1], D, Wact + lay.wdn[l], D, dpre[l], FF, upre[l], FF, N, FF, D, 0), {g}, {});
       addp(s + "dWdown", mkgemm(GL_TN, wepi, uact[l], FF, dxs[l + 1], D, G(lay.wdn[l]), D, nullptr, 0, FF, D, N, 0), {g}, {});
+      if (interleave_adam) { if (l == L - 1) { if (!lay.tied) emit_adam_head(); } else emit_adam_layer(l + 1); }
       addp(s + "dln2", mkgemm(GL_NT, GE_STORE, dpre[l], FF, Wact + lay.wup[l], FF, dln2[l], D, nullptr, 0, N, D, FF, 0), {s + "dpre"}, {});
       addp(s + "dWup", mkgemm(GL_TN, wepi, ln2[l], D, dpre[l], FF, G(lay.wup[l]), FF, nullptr, 0, D, FF, N, 0), {s + "dpre"}, {});
       { PhaseDesc d = mk(TK_LN_BWD, rows16); d.p[0] = dh[l]; d.p[1] = dgp2[l]; d.p[2] = dln2[l]; d.p[3] = hb[l]; d.p[4] = mean2[l]; d.p[5] = rstd2[l]; d.p[6] = Wact + lay.g2[l]; d.p[7] = dxs[l + 1];
@@ -438,37 +489,16 @@ bool build_train_graph(ofa_ctx* c) {
     end_deps = {"loss mean", "embed bwd wte", "embed bwd wpe", "head dW", "head dX", "lnf dgamma"};
     for (int l = 0; l < L; l++) { const std::string s = "L" + std::to_string(l) + " "; for (const char* nm : {"dWdown", "dWup", "dgamma2", "dWo", "dWqkv", "dgamma1"}) end_deps.push_back(s + nm); }
     if (train) {
-      // ---- optimizer: one AdamW phase per parameter group, released as soon as that group's gradients are final
+      // ---- optimizer phases that were not already emitted inside the backward pass
       end_deps = {"loss mean"};
       if (ext) for (size_t bi = 0; bi < buckets.size(); bi++) {
         PhaseDesc d = mk(TK_EXT_WAIT, 1); d.p[0] = c->d_ext_done + bi;
         addp("allreduce done " + std::to_string(bi), d, {"grads ready " + std::to_string(bi)}, {});
       }
-      auto gate = [&](const std::string& adam_name, std::vector<std::string> deps) {
-        if (!ext) return deps;
-        for (size_t bi = 0; bi < buckets.size(); bi++) for (const std::string& a : buckets[bi].adam_phases) if (a == adam_name) return std::vector<std::string>{"allreduce done " + std::to_string(bi)};
-        return deps;
-      };
-      auto mkadam = [&](size_t off, size_t n, const std::vector<Span>& nodecay) {
-        PhaseDesc d = mk(TK_ADAMW, (int)((n + ew::OPT_CHUNK - 1) / ew::OPT_CHUNK));
-        d.p[0] = c->W32 + off; d.p[1] = G(off); d.p[2] = c->M32 + off; d.p[3] = c->V32 + off; d.p[4] = Wact + off;
-        d.n = n; d.i0 = (int)nodecay.size(); d.i1 = gbf ? 1 : 0;
-        std::vector<int2> nd; for (const Span& sp : nodecay) nd.push_back(make_int2((int)(sp.off - off), (int)(sp.off - off + sp.n)));
-        int2* dn = c->ar.alloc<int2>(std::max<size_t>(1, nd.size()));
-        if (dn && !nd.empty()) c->ar.h2d(dn, nd.data(), nd.size() * sizeof(int2));
-        d.p[5] = dn;
-        return d;
-      };
-      if (!lay.tied) { addp("adamw head", mkadam(lay.head, V * D, {}), gate("adamw head", {"head dW", "head dX"}), {}); end_deps.push_back("adamw head"); }
-      for (int l = L - 1; l >= 0; l--) {
-        const std::string s = "L" + std::to_string(l) + " ";
-        const size_t off = lay.g1[l], end = (l + 1 < L) ? lay.g1[l + 1] : lay.gf + D;
-        std::vector<Span> nd = {Span{lay.g1[l], D}, Span{lay.g2[l], D}};
-        std::vector<std::string> deps = {s + "dWdown", s + "dWup", s + "dgamma2", s + "dWo", s + "dWqkv", s + "dgamma1", s + "ln1 bwd"};
-        if (l == L - 1) { nd.push_back(Span{lay.gf, D}); deps.push_back("lnf dgamma"); }
-        addp("adamw L" + std::to_string(l), mkadam(off, end - off, nd), gate("adamw L" + std::to_string(l), deps), {});
-        end_deps.push_back("adamw L" + std::to_string(l));
-      }
+      if (!lay.tied && !id.count("adamw head")) emit_adam_head();
+      for (int l = L - 1; l >= 0; l--) if (!id.count("adamw L" + std::to_string(l))) emit_adam_layer(l);
+      if (!lay.tied) end_deps.push_back("adamw head");
+      for (int l = 0; l < L; l++) end_deps.push_back("adamw L" + std::to_string(l));
       addp("adamw wte", mkadam(lay.wte, V * D, {}), gate("adamw wte", {"embed bwd wte", "head dX", lay.tied ? "head dW" : ""}), {});
       addp("adamw wpe", mkadam(lay.wpe, (size_t)m.T * D, {}), gate("adamw wpe", {"embed bwd wpe"}), {});
       end_deps.push_back("adamw wte"); end_deps.push_back("adamw wpe");
@@ -730,11 +760,11 @@ extern "C" int ofa_create(const ofa_config* cfg, ofa_ctx** out) {
   }
   const int nph = std::max<int>(1, (int)c->train_ph.size());
   c->d_phase_busy = c->ar.alloc<unsigned long long>(nph); c->d_phase_first = c->ar.alloc<unsigned long long>(nph); c->d_phase_last = c->ar.alloc<unsigned long long>(nph);
-  c->d_blk_busy = c->ar.alloc<unsigned long long>(2 * c->nblocks);
+  c->d_blk_busy = c->ar.alloc<unsigned long long>(6 * c->nblocks);
   if (!c->ar.ok) return bail(OFA_CUDA_ERROR, "out of device memory");
   c->d_dec_phase_busy = c->ar.alloc<unsigned long long>(std::max<size_t>(1, c->dec_ph.size()));
   c->d_blk_info = c->ar.alloc<int>(c->nblocks); C.blk_info = c->d_blk_info;
-  C.phase_busy = c->d_phase_busy; C.phase_first = c->d_phase_first; C.phase_last = c->d_phase_last; C.blk_busy = c->d_blk_busy; C.dec_phase_busy = c->d_dec_phase_busy;
+  C.phase_busy = c->d_phase_busy; C.phase_first = c->d_phase_first; C.phase_last = c->d_phase_last; C.blk_busy = c->d_blk_busy; C.blk_wait = c->d_blk_busy + 2 * c->nblocks; C.dec_phase_busy = c->d_dec_phase_busy;
   *out = c;
   return OFA_OK;
 }
@@ -852,7 +882,7 @@ extern "C" int ofa_launch(ofa_ctx* c, int nsteps) {
   cudaMemsetAsync(c->d_finished, 0, 2 * sizeof(int), c->stream);
   C.arrived = c->d_finished + 1;
   cudaMemsetAsync(c->d_phase_busy, 0, sizeof(unsigned long long) * std::max<size_t>(1, c->train_ph.size()), c->stream);
-  cudaMemsetAsync(c->d_blk_busy, 0, sizeof(unsigned long long) * 2 * c->nblocks, c->stream);
+  cudaMemsetAsync(c->d_blk_busy, 0, sizeof(unsigned long long) * 6 * c->nblocks, c->stream);
   cudaMemsetAsync(c->d_dec_phase_busy, 0, sizeof(unsigned long long) * std::max<size_t>(1, c->dec_ph.size()), c->stream);
   C.smem_bytes = c->smem;
   const Ctx& L = C;
@@ -924,7 +954,7 @@ extern "C" int ofa_phase_info(const ofa_ctx* c, int phase, char* name, size_t na
   return OFA_OK;
 }
 extern "C" int ofa_read_block_busy(ofa_ctx* c, unsigned long long* out, size_t n) {
-  if (!c || !out || c->dry || n > (size_t)2 * c->nblocks) return fail(c, OFA_BAD_ARGUMENT, "bad request");
+  if (!c || !out || c->dry || n > (size_t)6 * c->nblocks) return fail(c, OFA_BAD_ARGUMENT, "bad request");
   if (c->in_flight) return fail(c, OFA_BAD_ARGUMENT, "launch in flight");
   cudaSetDevice(c->device);
   return cudaMemcpy(out, c->d_blk_busy, n * 8, cudaMemcpyDeviceToHost) == cudaSuccess ? OFA_OK : fail(c, OFA_CUDA_ERROR, "D2H failed");
@@ -1028,7 +1058,7 @@ extern "C" int ofa_run_phases(int dtype, const ofa_dims* dims, const ofa_phase* 
       case TK_ATT_PREP: d.ntasks = bf ? BH * (m.T / attn::QTILE) : 1; break;
       case TK_ATT_BWD: d.ntasks = bf ? 2 * BH * (m.T / attn::QTILE) : BH; break;
       case TK_CE: d.ntasks = (m.N + ew::CE_ROWS - 1) / ew::CE_ROWS;
-        d.i0 = (int)(std::min<size_t>((size_t)((bf ? gemm_tc::BAR_OFFSET : smem - 256) - 64), (size_t)m.V * (bf ? 2 : 4)) / 16 * 16); break;
+        d.i0 = (int)(std::min<size_t>((size_t)((bf ? gemm_tc::BAR_OFFSET : smem - 512) - 64), (size_t)m.V * (bf ? 2 : 4)) / 16 * 16); break;
       case TK_CE_MEAN: case TK_BARRIER: d.ntasks = 1; break;
       case TK_EMB_WTE: d.ntasks = (m.V + ew::EMB_VCHUNK - 1) / ew::EMB_VCHUNK; break;
       case TK_EMB_WPE: d.ntasks = (m.T + ew::WPE_ROWS - 1) / ew::WPE_ROWS; break;

@@ -34,6 +34,7 @@ enum TaskKind : int {
   TK_DEC_HEAD,
   TK_DEC_SAMPLE,
   TK_EXT_WAIT,     // 1 task: wait (bounded) until an external 32-bit flag >= step_base+step+1 (gradient all-reduce finished)
+  TK_SUMCAST,      // out[i] = act(sum of i0 fp32 partial buffers p[1..]) over n elements (split-K reduce)
   TK_EXT_SIGNAL,   // 1 task: store step_base+step+1 to an external 32-bit flag (gradient bucket ready)
   TK_COUNT
 };
@@ -133,6 +134,7 @@ struct Ctx {
   int* tok_in; int* tok_tgt;
   int step_base;            // steps completed by earlier launches: added to the step index for data windows, LR and AdamW
   unsigned long long *phase_busy, *phase_first, *phase_last; int prof_step;
+  unsigned long long* blk_wait;         // per block: time its thread 0 spent waiting for training dependencies (ns)
   unsigned long long* dec_phase_busy;   // per serving phase: summed task time (ns)
   unsigned long long* step_done; float* loss_hist; unsigned long long* blk_busy; int* finished; unsigned long long* t_end;
   int infer_sms, reserved_sms, train_sms, use_decode, use_train;
@@ -143,7 +145,7 @@ struct Ctx {
   unsigned long long dep_timeout_ns;
   int* blk_info;            // per block: %smid | role << 16 (1 serve, 2 reserved-idle, 3 train, 4 idle)
   int* arrived;             // blocks of this launch that have started (idle partitions leave only when all have)
-  int smem_bytes;           // dynamic shared memory per block; its last 256 bytes hold barriers (tensor-core path) and the scheduler's hand-off words
+  int smem_bytes;           // dynamic shared memory per block; its last 512 bytes hold barriers (tensor-core path), the scheduler's hand-off words and the current phase descriptor
 };
 
 }  // namespace ofa

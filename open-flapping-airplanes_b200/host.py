@@ -156,6 +156,12 @@ class Megakernel:
         self._chk(self.lib.ofa_read_block_busy(self.h, out.ctypes.data_as(C.c_void_p), out.size))
         return out.reshape(nblocks, 2)
 
+    def block_wait_ns(self, nblocks=296):
+        """rows: dependency wait, claim, hand-off to the block, completion signalling (ns per block, training job)"""
+        out = np.zeros(6 * nblocks, dtype=np.uint64)
+        self._chk(self.lib.ofa_read_block_busy(self.h, out.ctypes.data_as(C.c_void_p), out.size))
+        return out[2 * nblocks:].reshape(4, nblocks)
+
     def block_info(self, nblocks=296):
         """(smid, role) per block of the last launch; role 1 serving, 2 reserved, 3 training, 4 idle"""
         out = np.zeros(nblocks, dtype=np.int32)

@@ -160,6 +160,7 @@ def test_bf16_loss_curve_and_repeatability(ofa, oracle):
 def test_gpt_s_full_size_properties(ofa, oracle):
     """BASELINE config 2 at full size: size-independent checks (the oracle would need minutes per step here)."""
     cfg = ofa.default_config("gpt_s")
+    cfg.adam_interleave, cfg.head_dx_splitk = 1, 1            # also exercises the optional graph variants at full size
     mk = ofa.Megakernel(cfg)
     assert mk.num_params == 163007232 + 0 * 768
     rng = np.random.default_rng(1234)

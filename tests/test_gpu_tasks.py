@@ -148,7 +148,7 @@ def test_adamw_three_steps(ofa, K, oracle, bf, gbf):
 
 GEMM_CASES = [  # (layout, epi, M, N, K)
     (0, 0, 256, 256, 128), (0, 1, 256, 384, 192), (0, 2, 128, 512, 64), (1, 0, 384, 256, 256), (1, 3, 256, 256, 128),
-    (2, 4, 256, 384, 512), (2, 0, 128, 128, 1024), (0, 0, 512, 2304, 768), (1, 0, 256, 50304, 768), (2, 4, 768, 768, 4096),
+    (2, 4, 256, 384, 512), (2, 0, 128, 128, 1024), (0, 4, 256, 256, 256), (0, 0, 512, 2304, 768), (1, 0, 256, 50304, 768), (2, 4, 768, 768, 4096),
 ]
 
 

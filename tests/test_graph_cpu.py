@@ -13,7 +13,7 @@ def plan(ofa, preset, **kw):
 
 
 @pytest.mark.parametrize("preset,kw", [("gpt_s", {}), ("gpt_s", dict(tied_head=1)), ("gpt_s", dict(mode=1)), ("gpt_s", dict(mode=2)),
-                                       ("gpt_s", dict(dp_world=8, grad_bf16=1, ext_sync=1)), ("tiny", {}), ("tiny", dict(tied_head=1)), ("tiny", dict(mode=2))])
+                                       ("gpt_s", dict(dp_world=8, grad_bf16=1, ext_sync=1)), ("gpt_s", dict(adam_interleave=1, head_dx_splitk=1)), ("tiny", {}), ("tiny", dict(tied_head=1)), ("tiny", dict(mode=2))])
 def test_training_graph_is_topologically_ordered(ofa, preset, kw):
     mk = plan(ofa, preset, **kw)
     ph = mk.phases()
@@ -51,14 +51,20 @@ def test_training_graph_is_topologically_ordered(ofa, preset, kw):
 
 
 def test_gpt_s_task_counts_and_layout(ofa):
-    mk = plan(ofa, "gpt_s")
+    mk = plan(ofa, "gpt_s", adam_interleave=1, head_dx_splitk=1)
     assert mk.num_params == 163007232
     ph = {p["name"]: p for p in mk.phases()}
     assert ph["embed"]["ntasks"] == 256 and ph["L0 ln1"]["ntasks"] == 256 and ph["cross-entropy"]["ntasks"] == 1024
     assert ph["L3 attn"]["ntasks"] == 4 * 12 * 8 and ph["L3 attn bwd"]["ntasks"] == 2 * 4 * 12 * 8
-    assert ph["L0 qkv"]["ntasks"] == 32 * 18 and ph["L0 dWo"]["ntasks"] == 36 and ph["embed bwd wte"]["ntasks"] == 393
+    assert (32 * 18) % ph["L0 qkv"]["ntasks"] == 0 and ph["L0 dWo"]["ntasks"] == 36 and ph["embed bwd wte"]["ntasks"] == 393   # GEMM tasks are strips of whole tiles
+    # head dX is cut along K into partial products that a reduce phase sums; its name stays the dependency target
+    names = list(ph)
+    parts = [n for n in names if n.startswith("head dX k")]
+    assert len(parts) in (2, 3, 4) and all(names.index(p) < names.index("head dX") for p in parts)
+    # a layer's AdamW sits inside the backward pass, below the layer it updates
+    assert names.index("adamw L11") < names.index("L10 dln2") and names.index("adamw L0") > names.index("L0 ln1 bwd")
     assert ph["adamw L5"]["ntasks"] == 109 and ph["adamw head"]["ntasks"] == 590 and ph["adamw wpe"]["ntasks"] == 12
-    assert 32 * 393 % ph["logits"]["ntasks"] == 0 or ph["logits"]["ntasks"] >= 32 * 393 // 4
+    assert 32 * 393 // 8 <= ph["logits"]["ntasks"] <= 32 * 393
     order = ["wte", "wpe", "lm_head"] + [f"L{l}.{t}" for l in range(12) for t in ("g1", "Wqkv", "Wo", "g2", "Wup", "Wdn")] + ["gf"]
     pos = 0
     for n in order:
