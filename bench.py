@@ -112,8 +112,9 @@ def cpu_step_tokens_per_s(max_seconds=30.0):
     opt = orc.make_optimizer(cfg, model)
     tokens = orc.synthetic_tokens(V, 1 << 16, 0)
     nseq, t_total, ntok = 0, 0.0, 0
-    # first sequence warms the allocator and is not counted; then as many sequences as fit in the time budget (at least one)
-    for i in range(1 + B):
+    # first sequence warms the allocator and is not counted; then as many sequences as fit in the time budget (at least one,
+    # at most 12 steps' worth)
+    for i in range(1 + 12 * B):
         seq = tokens[i * 1100:i * 1100 + T + 1].astype(np.int64)
         x = torch.from_numpy(seq[None, :-1]).contiguous(); y = torch.from_numpy(seq[None, 1:]).contiguous()
         t0 = time.perf_counter()
@@ -274,10 +275,10 @@ def main():
             cat = {}
             for p in mk.phases():
                 key = re.sub(r"^L\d+ ", "L* ", p["name"]); key = re.sub(r"adamw L\d+", "adamw L*", key)
-                c = cat.setdefault(key, [0, 0]); c[0] += p["busy_ns"]; c[1] += p["ntasks"]
-            print("  per category (block-ms per step, share of busy, mean us per task):", file=sys.stderr)
-            for k, (b, n) in sorted(cat.items(), key=lambda kv: -kv[1][0]):
-                print(f"    {k:22s} {b / 1e6 / K:8.3f}  {100.0 * b / tot:5.1f} %  {b / 1e3 / K / max(1, n):8.2f} us/task  ({n} tasks)", file=sys.stderr)
+                c = cat.setdefault(key, [0, 0, 0]); c[0] += p["busy_ns"]; c[1] += p["ntasks"]; c[2] += p["wait_ns"]
+            print("  per category (block-ms per step, share of busy, mean us per task, block-ms per step waiting for its dependencies):", file=sys.stderr)
+            for k, (b, n, w) in sorted(cat.items(), key=lambda kv: -kv[1][0]):
+                print(f"    {k:22s} {b / 1e6 / K:8.3f}  {100.0 * b / tot:5.1f} %  {b / 1e3 / K / max(1, n):8.2f} us/task  ({n} tasks)  wait {w / 1e6 / K:8.3f}", file=sys.stderr)
             for p in sorted(mk.phases(), key=lambda p: -p["busy_ns"])[:40]:
                 print(f"  {p['name']:24s} tasks {p['ntasks']:6d}  busy {p['busy_ns'] / 1e6 / K:8.3f} ms/step  {100.0 * p['busy_ns'] / tot:5.1f} %", file=sys.stderr)
         if world == 1 and not args.no_cpu_baseline:

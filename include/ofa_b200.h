@@ -112,6 +112,8 @@ int ofa_read_losses(ofa_ctx* ctx, float* out, size_t n);                  /* los
 int ofa_read_step_times(ofa_ctx* ctx, unsigned long long* out, size_t n); /* %globaltimer ns at the end of each step of the last launch */
 int ofa_num_phases(const ofa_ctx* ctx);
 int ofa_phase_info(const ofa_ctx* ctx, int phase, char* name, size_t name_cap, int* kind, int* ntasks, unsigned long long* busy_ns);
+/* nanoseconds the training blocks spent waiting for the dependencies of tasks of this phase during the last launch (summed over blocks): shows which phase boundaries the step loses time at; no counterpart in the reference's report */
+int ofa_phase_wait_ns(const ofa_ctx* ctx, int phase, unsigned long long* wait_ns);
 /* busy nanoseconds of every block in the last launch: out[2*block + job] (job 0 training, 1 serving) for the first 2*grid entries (ofa.cu:313 blk_busy), then four rows of grid entries each: time the block's scheduler thread spent waiting for training dependencies, claiming tickets, handing the task to the block, and signalling completion; n <= 6 * grid size */
 int ofa_read_block_busy(ofa_ctx* ctx, unsigned long long* out, size_t n);
 /* in-kernel trace of the serving job (the reference's DTRACE, decode_wide.cuh:11-16): %globaltimer stamps of the stage boundaries inside task 0 of layer 0 (slots 0-4 QKV, 8-12 UP+DOWN, 16-19 scheduler-side start/end of those tasks), last token of the last launch */

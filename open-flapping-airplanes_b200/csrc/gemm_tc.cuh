@@ -38,8 +38,8 @@ constexpr int PIPE_BYTES = 96 * 1024;                // 3 stages x 32 KB (BN 128
 constexpr int EPI_WARPS = 4;                         // warps 4..7
 constexpr int STAGING_BYTES = EPI_WARPS * 32 * 32 * 4;   // 16 KB
 constexpr int BAR_OFFSET = PIPE_BYTES + STAGING_BYTES;   // control area: barriers, TMEM slot, scheduler words
-constexpr int BAR_BYTES = 512;
-constexpr int SMEM_BYTES = BAR_OFFSET + BAR_BYTES;   // 115,200 B: two blocks per SM
+constexpr int BAR_BYTES = CTRL_BYTES;
+constexpr int SMEM_BYTES = BAR_OFFSET + BAR_BYTES;   // 115,712 B: two blocks per SM use the whole 228 KB (1 KB per block is reserved by the system)
 constexpr int TMEM_COLS = 256;
 
 template <int BN> struct Cfg {
@@ -51,10 +51,11 @@ template <int BN> struct Cfg {
   static constexpr int BAR0 = BN == 128 ? 0 : 176;                // byte offset of this width's barriers in the control area
   static_assert(STAGES * STAGE_BYTES <= PIPE_BYTES, "pipeline does not fit");
 };
-// control area (512 B at smem + BAR_OFFSET = the last 512 bytes of dynamic shared memory):
+// control area (1 KB at smem + BAR_OFFSET = the last 1,024 bytes of dynamic shared memory):
 //   [  0, 80) BN128: full[3] empty[3] accf[2] acce[2]     [ 80, 84) TMEM base slot     [ 96,104) serving fill barrier
 //   [128,160) scheduler hand-off words                      [176,224) BN256: full[2] empty[2] accf[1] acce[1]
-//   [256,512) the block's copy of the phase descriptor it is working on
+//   [256,512) and [512,768) two slots for phase descriptors: the one being worked on and the next phase's, fetched ahead
+//   [768,832) scheduling record (ticket range + dependencies) of the phase the scheduler thread looks at next
 template <int BN> __device__ __forceinline__ uint32_t bar_full(uint32_t base, int s) { return base + BAR_OFFSET + Cfg<BN>::BAR0 + 8u * s; }
 template <int BN> __device__ __forceinline__ uint32_t bar_empty(uint32_t base, int s) { return base + BAR_OFFSET + Cfg<BN>::BAR0 + 8u * (Cfg<BN>::STAGES + s); }
 template <int BN> __device__ __forceinline__ uint32_t bar_accf(uint32_t base, int b) { return base + BAR_OFFSET + Cfg<BN>::BAR0 + 8u * (2 * Cfg<BN>::STAGES + b); }

@@ -150,13 +150,39 @@ __device__ __forceinline__ void run_decode_task(const Ctx& C, const PhaseDesc& d
 // ---------------------------------------------------------------------------------------------- scheduler
 // Dependency wait of thread 0 (bounded). Returns 0 when every dependency of (step, ph) is satisfied, -2 when the block must
 // leave (job finished elsewhere, abort, or deadline).
-__device__ __forceinline__ int wait_deps(const Ctx& C, const Job& J, int job_id, int step, int ph, int local) {
-  const int off = __ldg(J.dep_off + ph), cnt = __ldg(J.dep_cnt + ph);
+__device__ __forceinline__ int wait_deps(const Ctx& C, const Job& J, int job_id, int step, int ph, int local, const volatile int* rec) {
+  const int cnt = rec[2];
   const u64 t0 = gtimer();
   unsigned spins = 0;
+  if (cnt >= 0) {
+    // up to four dependencies from the phase's scheduling record: their counters are read with relaxed loads that are all in
+    // flight together, and one acquire fence after the last successful check orders the task's reads behind them
+    int need[4]; const int* ctr[4];
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+      const int p = k < cnt ? rec[4 + 3 * k] : 0, dl = k < cnt ? rec[5 + 3 * k] : 0, nt = k < cnt ? rec[6 + 3 * k] : 0;
+      ctr[k] = J.done + p; need[k] = k < cnt ? nt * (step + 1 + dl) : 0;
+    }
+    for (;;) {
+      int v[4];
+#pragma unroll
+      for (int k = 0; k < 4; k++) v[k] = need[k] > 0 ? ld_relaxed(ctr[k]) : 0;
+      bool ready = true;
+#pragma unroll
+      for (int k = 0; k < 4; k++) ready = ready && v[k] >= need[k];
+      if (ready) { fence_acquire(); return 0; }
+      if (job_id == 1 && C.use_train && ld_relaxed(C.finished)) return -2;
+      if ((++spins & 63u) == 0) {
+        if (aborted(C.status)) return -2;
+        if (gtimer() - t0 > C.dep_timeout_ns) { raise_abort(C.status, ST_DEP_TIMEOUT, ph, local, step); return -2; }
+      }
+      __nanosleep(job_id == 1 ? 20 : 80);
+    }
+  }
+  const int off = __ldg(J.dep_off + ph), n = __ldg(J.dep_cnt + ph);
   for (;;) {
     bool ready = true;
-    for (int k = 0; k < cnt && ready; k++) {
+    for (int k = 0; k < n && ready; k++) {
       const Dep e = J.deps[off + k];
       const int need = __ldg(J.ntasks + e.phase) * (step + 1 + e.delta);
       if (need > 0 && ld_acquire(J.done + e.phase) < need) ready = false;
@@ -171,13 +197,28 @@ __device__ __forceinline__ int wait_deps(const Ctx& C, const Job& J, int job_id,
   }
 }
 
+__device__ __forceinline__ void sched_cp16(uint32_t dst, const void* src) { asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory"); }
+__device__ __forceinline__ void sched_cp_wait() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
 template <class T, int D, int DH>
 __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* smem) {
-  unsigned char* ctrl = smem + C.smem_bytes - 512;   // the last 512 bytes of dynamic shared memory are the block's control area (map in gemm_tc.cuh)
+  unsigned char* ctrl = smem + C.smem_bytes - CTRL_BYTES;   // the last bytes of dynamic shared memory are the block's control area (map in gemm_tc.cuh)
   volatile int* s_sel = reinterpret_cast<volatile int*>(ctrl + 128);
-  PhaseDesc* s_desc = reinterpret_cast<PhaseDesc*>(ctrl + 256);
-  static_assert(sizeof(PhaseDesc) <= 256, "descriptor copy does not fit the control area");
-  int cached_ph = -1;
+  static_assert(sizeof(PhaseDesc) <= 256 && sizeof(PhaseDesc) % 16 == 0, "descriptor copy does not fit the control area");
+  static_assert(sizeof(SchedRec) == 64, "scheduling record is one 64-byte line");
+  int slot = 0;                                     // which of the two descriptor slots holds the phase being worked on
+  int cached_ph = -1, ahead_ph = -1;                // phases held by that slot and by the other one (fetched ahead)
+  volatile int* s_rec = reinterpret_cast<volatile int*>(ctrl + 768);
+  const uint32_t s_rec_addr = smem_u32(ctrl + 768);
+  int rec_ph = -1;                                  // thread 0: the phase whose record is (or is on its way) in s_rec
+  auto need_rec = [&](int p) {                      // thread 0: make s_rec hold phase p's record
+    if (rec_ph != p) {
+#pragma unroll
+      for (int q = 0; q < 4; q++) sched_cp16(s_rec_addr + 16 * q, reinterpret_cast<const char*>(J.rec + p) + 16 * q);
+      rec_ph = p;
+    }
+    sched_cp_wait();
+  };
   const int tid = threadIdx.x;
   u64 busy = 0;
   int rstep = -1, rph = -1;                         // thread 0: the (step, phase) last seen ready
@@ -194,9 +235,8 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
     __syncthreads();
   }
   u64 waited = 0, t_claim = 0, t_sync = 0, t_tail = 0, tl0 = 0, tl1 = 0;   // thread 0: where the time outside tasks goes
-  int c_ph = 0, c_lo = 0, c_hi = 0;                  // thread 0: cached phase and its ticket range [c_lo, c_hi) within a step
+  int c_ph = -1, c_lo = 0, c_hi = 0;                 // thread 0: cached phase and its ticket range [c_lo, c_hi) within a step
   unsigned next_g = 0; bool have_next = false; unsigned claims = 0;   // thread 0: the ticket taken at the end of the previous task
-  if (tid == 0) c_hi = __ldg(J.prefix + 1);
   for (;;) {
     if (tid == 0) {                                  // ---- claim (and, for the training job, wait for the dependencies)
       tl0 = gtimer(); if (tl1) t_tail += tl0 - tl1;
@@ -211,19 +251,23 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
         else {
           step = (int)(g / (unsigned)J.tasks_per_step);
           const int r = (int)(g - (unsigned)step * (unsigned)J.tasks_per_step);
-          // tickets of a block mostly stay in the phase of its previous ticket or move a few phases on: keep that phase's
-          // bounds in registers and walk forward; fall back to a binary search only when the ticket lies before them
-          if (r < c_lo) {
-            int lo = 0, hi = J.nph;                 // last phase whose prefix <= r
-            while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if (__ldg(J.prefix + mid) <= r) lo = mid; else hi = mid; }
-            c_ph = lo; c_lo = __ldg(J.prefix + lo); c_hi = __ldg(J.prefix + lo + 1);
+          // A block's tickets grow, so within a step it only moves forward through the phases: keep the current phase's
+          // ticket range in registers and walk on, one scheduling record per phase passed. The record of the phase after
+          // the one just worked on was requested at the end of the previous task and is normally already in shared memory.
+          if (r < c_lo) { c_ph = -1; c_lo = 0; c_hi = 0; }        // a new step
+          while (r >= c_hi) {
+            c_ph++;
+            need_rec(c_ph);
+            c_lo = s_rec[0]; c_hi = s_rec[1];
           }
-          while (r >= c_hi) { c_ph++; c_lo = c_hi; c_hi = __ldg(J.prefix + c_ph + 1); }
           ph = c_ph; local = r - c_lo;
           if (job_id == 0 && !(step == rstep && ph == rph)) {
             const u64 w0 = gtimer();
-            res = wait_deps(C, J, job_id, step, ph, local);
-            waited += gtimer() - w0;
+            need_rec(ph);
+            res = wait_deps(C, J, job_id, step, ph, local, s_rec);
+            const u64 w = gtimer() - w0;
+            waited += w;
+            if (C.phase_busy && w > 200) atomicAdd(C.phase_busy + J.nph + ph, w);
             if (res == 0) { rstep = step; rph = ph; }
           }
         }
@@ -235,21 +279,24 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
     int res = s_sel[0];
     const int step = s_sel[1], ph = s_sel[2], local = s_sel[3];
     if (res < 0) break;
-    // The descriptor is fetched once per phase change with one coalesced load and then read from shared memory: every
-    // dependency check ends with a device-scope acquire, after which L1 no longer holds it, and the chain of dependent global
-    // loads that decoding it would take was a measurable part of the per-task overhead.
+    // The descriptor is read from shared memory: every dependency check ends with a device-scope acquire, after which L1 no
+    // longer holds it, and the chain of dependent global loads that decoding it would take was a measurable part of the
+    // per-task overhead. Two slots: the next phase's descriptor is requested at the end of a task (below), so a block that
+    // moves on by one phase - the common case when phases have about as many tasks as there are blocks - finds it here.
+    if (tid < 16) sched_cp_wait();
     if (ph != cached_ph) {
-      if (tid < (int)(sizeof(PhaseDesc) / 4)) reinterpret_cast<uint32_t*>(s_desc)[tid] = __ldg(reinterpret_cast<const uint32_t*>(J.ph + ph) + tid);
+      if (ph == ahead_ph) { slot ^= 1; ahead_ph = cached_ph; }
+      else if (tid < (int)(sizeof(PhaseDesc) / 4)) reinterpret_cast<uint32_t*>(ctrl + 256 + 256 * slot)[tid] = __ldg(reinterpret_cast<const uint32_t*>(J.ph + ph) + tid);
       cached_ph = ph;
       __syncthreads();
     }
-    const PhaseDesc& d = *s_desc;
+    const PhaseDesc& d = *reinterpret_cast<const PhaseDesc*>(ctrl + 256 + 256 * slot);
     bool filled = false;
     if (job_id == 1) {                               // ---- serving: start the weight prefetch, THEN wait for the dependencies
       filled = dec::prefetch<T, D, DH>(C.dp, C.md, d.kind, d.i0, local, smem, fill_bar);
       if (tid == 0) {
         int r2 = 0;
-        if (!(step == rstep && ph == rph)) { r2 = wait_deps(C, J, job_id, step, ph, local); if (r2 == 0) { rstep = step; rph = ph; } }
+        if (!(step == rstep && ph == rph)) { need_rec(ph); r2 = wait_deps(C, J, job_id, step, ph, local, s_rec); if (r2 == 0) { rstep = step; rph = ph; } }
         s_sel[4] = r2;
       }
       __syncthreads();
@@ -268,6 +315,19 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
     else run_decode_task<T, D, DH>(C, d, local, smem, fill_bar, fills & 1u);
     if (filled) fills++;
     __syncthreads();
+    {                                                // ask for the next phase's descriptor and scheduling record now
+      const int nxt = ph + 1 < J.nph ? ph + 1 : 0;
+      if (nxt != ahead_ph) {
+        if (tid >= 1 && tid <= (int)(sizeof(PhaseDesc) / 16))
+          sched_cp16(smem_u32(ctrl + 256 + 256 * (slot ^ 1)) + 16 * (tid - 1), reinterpret_cast<const char*>(J.ph + nxt) + 16 * (tid - 1));
+        ahead_ph = nxt;
+      }
+      if (tid == 0 && rec_ph != nxt) {
+#pragma unroll
+        for (int q = 0; q < 4; q++) sched_cp16(s_rec_addr + 16 * q, reinterpret_cast<const char*>(J.rec + nxt) + 16 * q);
+        rec_ph = nxt;
+      }
+    }
     if (tid == 0) {
       // Completion signal first: a release at device scope after the block barrier orders every thread's writes of this task
       // before it (no separate fence, and nobody waits for its round trip). The step's last phase needs the old value.
@@ -294,6 +354,7 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
       }
     }
   }
+  sched_cp_wait();
   if (use_tc) gemm_tc::block_exit(gp, smem, C.status);
   if (tid == 0 && C.blk_busy) { C.blk_busy[blockIdx.x * 2 + job_id] = busy; if (job_id == 0 && C.blk_wait) { C.blk_wait[blockIdx.x] = waited; C.blk_wait[gridDim.x + blockIdx.x] = t_claim; C.blk_wait[2 * gridDim.x + blockIdx.x] = t_sync; C.blk_wait[3 * gridDim.x + blockIdx.x] = t_tail; } }
 }

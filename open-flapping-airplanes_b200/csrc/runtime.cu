@@ -24,11 +24,11 @@ struct HostPhase { std::string name; PhaseDesc d; std::vector<Dep> deps; };
 
 struct DevJob {
   Job j{};
-  PhaseDesc* ph = nullptr; int *prefix = nullptr, *ntasks = nullptr, *dep_off = nullptr, *dep_cnt = nullptr; Dep* deps = nullptr;
+  PhaseDesc* ph = nullptr; SchedRec* rec = nullptr; int *prefix = nullptr, *ntasks = nullptr, *dep_off = nullptr, *dep_cnt = nullptr; Dep* deps = nullptr;
   int* done = nullptr; unsigned* ticket = nullptr;
   int nph = 0;
   void free_all() {
-    cudaFree(ph); cudaFree(prefix); cudaFree(ntasks); cudaFree(dep_off); cudaFree(dep_cnt); cudaFree(deps); cudaFree(done); cudaFree(ticket);
+    cudaFree(ph); cudaFree(rec); rec = nullptr; cudaFree(prefix); cudaFree(ntasks); cudaFree(dep_off); cudaFree(dep_cnt); cudaFree(deps); cudaFree(done); cudaFree(ticket);
     *this = DevJob();
   }
 };
@@ -164,14 +164,24 @@ bool upload_job(const std::vector<HostPhase>& ph, int last_phase, int nsteps, De
     if (nt[i] <= 0) { err = "phase without tasks: " + ph[i].name; return false; }
   }
   if ((double)prefix[nph] * (double)nsteps >= 4.0e9) { err = "ticket counter would overflow"; return false; }
+  std::vector<SchedRec> rec(nph);
+  for (int i = 0; i < nph; i++) {
+    SchedRec& r = rec[i]; memset(&r, 0, sizeof(r));
+    r.lo = prefix[i]; r.hi = prefix[i + 1];
+    const int n = (int)ph[i].deps.size();
+    r.ndeps = n <= 4 ? n : -1;
+    for (int k = 0; k < n && n <= 4; k++) { r.dep[3 * k] = ph[i].deps[k].phase; r.dep[3 * k + 1] = ph[i].deps[k].delta; r.dep[3 * k + 2] = nt[ph[i].deps[k].phase]; }
+  }
   if (deps.empty()) deps.push_back(Dep{0, 0});
   dj.free_all();
   bool ok = cudaMalloc(&dj.ph, sizeof(PhaseDesc) * nph) == cudaSuccess && cudaMalloc(&dj.prefix, 4 * (nph + 1)) == cudaSuccess &&
             cudaMalloc(&dj.ntasks, 4 * nph) == cudaSuccess && cudaMalloc(&dj.dep_off, 4 * nph) == cudaSuccess &&
             cudaMalloc(&dj.dep_cnt, 4 * nph) == cudaSuccess && cudaMalloc(&dj.deps, sizeof(Dep) * deps.size()) == cudaSuccess &&
-            cudaMalloc(&dj.done, 4 * nph) == cudaSuccess && cudaMalloc(&dj.ticket, 4) == cudaSuccess;
+            cudaMalloc(&dj.done, 4 * nph) == cudaSuccess && cudaMalloc(&dj.ticket, 4) == cudaSuccess &&
+            cudaMalloc(&dj.rec, sizeof(SchedRec) * nph) == cudaSuccess;
   if (!ok) { err = "cudaMalloc failed (job tables)"; return false; }
   cudaMemcpy(dj.ph, pd.data(), sizeof(PhaseDesc) * nph, cudaMemcpyHostToDevice);
+  cudaMemcpy(dj.rec, rec.data(), sizeof(SchedRec) * nph, cudaMemcpyHostToDevice);
   cudaMemcpy(dj.prefix, prefix.data(), 4 * (nph + 1), cudaMemcpyHostToDevice);
   cudaMemcpy(dj.ntasks, nt.data(), 4 * nph, cudaMemcpyHostToDevice);
   cudaMemcpy(dj.dep_off, doff.data(), 4 * nph, cudaMemcpyHostToDevice);
@@ -180,7 +190,7 @@ bool upload_job(const std::vector<HostPhase>& ph, int last_phase, int nsteps, De
   cudaMemset(dj.done, 0, 4 * nph); cudaMemset(dj.ticket, 0, 4);
   dj.nph = nph;
   dj.j.nph = nph; dj.j.tasks_per_step = prefix[nph]; dj.j.nsteps = nsteps; dj.j.last_phase = last_phase;
-  dj.j.ph = dj.ph; dj.j.prefix = dj.prefix; dj.j.ntasks = dj.ntasks; dj.j.dep_off = dj.dep_off; dj.j.dep_cnt = dj.dep_cnt; dj.j.deps = dj.deps;
+  dj.j.ph = dj.ph; dj.j.prefix = dj.prefix; dj.j.ntasks = dj.ntasks; dj.j.dep_off = dj.dep_off; dj.j.dep_cnt = dj.dep_cnt; dj.j.deps = dj.deps; dj.j.rec = dj.rec;
   dj.j.done = dj.done; dj.j.ticket = dj.ticket;
   return true;
 }
@@ -203,7 +213,7 @@ int smem_for(bool bf, int Tctx, int N) {
   m = std::max(m, ew::ln_bwd_smem_bytes<64>());
   m = std::max(m, dec::smem_bytes<float, 64, 16>(Tctx));
   m = std::max(m, (size_t)64 + 4096);
-  return (int)((m + 1023) / 1024 * 1024) + 512;   // + control area
+  return (int)((m + 1023) / 1024 * 1024) + CTRL_BYTES;   // + control area
 }
 
 }  // namespace
@@ -291,7 +301,7 @@ bool build_train_graph(ofa_ctx* c) {
     PhaseDesc d = mk(TK_GEMM, 0); d.layout = layout; d.epi = epi;
     d.g.A = A; d.g.B = B; d.g.C = Cc; d.g.aux = aux; d.g.M = M; d.g.N = Nn; d.g.K = K; d.g.lda = lda; d.g.ldb = ldb; d.g.ldc = ldc; d.g.ldaux = ldaux;
     d.g.accumulate = accumulate;
-    if (bf) { std::string e; if (!prepare_gemm_bf16(d, c->ar, cfg.gemm_nsub, c->nblocks, e)) { ok = false; err = e; } }
+    if (bf) { std::string e; if (!prepare_gemm_bf16(d, c->ar, cfg.gemm_nsub, c->C.train_sms > 0 ? 2 * c->C.train_sms : c->nblocks, e)) { ok = false; err = e; } }   // waves are counted over the blocks that train
     else prepare_gemm_f32(d);
     return d;
   };
@@ -361,7 +371,7 @@ bool build_train_graph(ofa_ctx* c) {
     end_deps = {"logits"};
   } else {
     { PhaseDesc d = mk(TK_CE, (int)((N + ew::CE_ROWS - 1) / ew::CE_ROWS)); d.p[0] = logits; d.p[1] = c->C.tok_tgt; d.p[2] = lossv;
-      const size_t usable = (size_t)((bf ? gemm_tc::BAR_OFFSET : c->smem - 512) - 64);
+      const size_t usable = (size_t)((bf ? gemm_tc::BAR_OFFSET : c->smem - CTRL_BYTES) - 64);
       d.i0 = (int)(std::min(usable, V * sizeof(T)) / 16 * 16);
       addp("cross-entropy", d, {"logits", "data"}, {}); }
     { PhaseDesc d = mk(TK_CE_MEAN, 1); d.p[0] = meanloss; d.p[1] = lossv; addp("loss mean", d, {"cross-entropy"}, {}); }
@@ -759,7 +769,7 @@ extern "C" int ofa_create(const ofa_config* cfg, ofa_ctx** out) {
     if (!ok) return bail(OFA_BAD_CONFIG, "decode graph: " + c->err);
   }
   const int nph = std::max<int>(1, (int)c->train_ph.size());
-  c->d_phase_busy = c->ar.alloc<unsigned long long>(nph); c->d_phase_first = c->ar.alloc<unsigned long long>(nph); c->d_phase_last = c->ar.alloc<unsigned long long>(nph);
+  c->d_phase_busy = c->ar.alloc<unsigned long long>(2 * nph);   /* busy, then dependency wait */ c->d_phase_first = c->ar.alloc<unsigned long long>(nph); c->d_phase_last = c->ar.alloc<unsigned long long>(nph);
   c->d_blk_busy = c->ar.alloc<unsigned long long>(6 * c->nblocks);
   if (!c->ar.ok) return bail(OFA_CUDA_ERROR, "out of device memory");
   c->d_dec_phase_busy = c->ar.alloc<unsigned long long>(std::max<size_t>(1, c->dec_ph.size()));
@@ -881,7 +891,7 @@ extern "C" int ofa_launch(ofa_ctx* c, int nsteps) {
   cudaMemsetAsync(c->d_status, 0, sizeof(DevStatus), c->stream);
   cudaMemsetAsync(c->d_finished, 0, 2 * sizeof(int), c->stream);
   C.arrived = c->d_finished + 1;
-  cudaMemsetAsync(c->d_phase_busy, 0, sizeof(unsigned long long) * std::max<size_t>(1, c->train_ph.size()), c->stream);
+  cudaMemsetAsync(c->d_phase_busy, 0, sizeof(unsigned long long) * 2 * std::max<size_t>(1, c->train_ph.size()), c->stream);
   cudaMemsetAsync(c->d_blk_busy, 0, sizeof(unsigned long long) * 6 * c->nblocks, c->stream);
   cudaMemsetAsync(c->d_dec_phase_busy, 0, sizeof(unsigned long long) * std::max<size_t>(1, c->dec_ph.size()), c->stream);
   C.smem_bytes = c->smem;
@@ -952,6 +962,12 @@ extern "C" int ofa_phase_info(const ofa_ctx* c, int phase, char* name, size_t na
   if (ntasks) *ntasks = p.d.ntasks;
   if (busy_ns) { if (c->dry) *busy_ns = 0; else { cudaSetDevice(c->device); cudaMemcpy(busy_ns, c->d_phase_busy + phase, 8, cudaMemcpyDeviceToHost); } }
   return OFA_OK;
+}
+extern "C" int ofa_phase_wait_ns(const ofa_ctx* c, int phase, unsigned long long* wait_ns) {
+  if (!c || !wait_ns || phase < 0 || phase >= (int)c->train_ph.size()) return OFA_BAD_ARGUMENT;
+  if (c->dry) { *wait_ns = 0; return OFA_OK; }
+  cudaSetDevice(c->device);
+  return cudaMemcpy(wait_ns, c->d_phase_busy + c->train_ph.size() + phase, 8, cudaMemcpyDeviceToHost) == cudaSuccess ? OFA_OK : OFA_CUDA_ERROR;
 }
 extern "C" int ofa_read_block_busy(ofa_ctx* c, unsigned long long* out, size_t n) {
   if (!c || !out || c->dry || n > (size_t)6 * c->nblocks) return fail(c, OFA_BAD_ARGUMENT, "bad request");
@@ -1058,7 +1074,7 @@ extern "C" int ofa_run_phases(int dtype, const ofa_dims* dims, const ofa_phase* 
       case TK_ATT_PREP: d.ntasks = bf ? BH * (m.T / attn::QTILE) : 1; break;
       case TK_ATT_BWD: d.ntasks = bf ? 2 * BH * (m.T / attn::QTILE) : BH; break;
       case TK_CE: d.ntasks = (m.N + ew::CE_ROWS - 1) / ew::CE_ROWS;
-        d.i0 = (int)(std::min<size_t>((size_t)((bf ? gemm_tc::BAR_OFFSET : smem - 512) - 64), (size_t)m.V * (bf ? 2 : 4)) / 16 * 16); break;
+        d.i0 = (int)(std::min<size_t>((size_t)((bf ? gemm_tc::BAR_OFFSET : smem - CTRL_BYTES) - 64), (size_t)m.V * (bf ? 2 : 4)) / 16 * 16); break;
       case TK_CE_MEAN: case TK_BARRIER: d.ntasks = 1; break;
       case TK_EMB_WTE: d.ntasks = (m.V + ew::EMB_VCHUNK - 1) / ew::EMB_VCHUNK; break;
       case TK_EMB_WPE: d.ntasks = (m.T + ew::WPE_ROWS - 1) / ew::WPE_ROWS; break;

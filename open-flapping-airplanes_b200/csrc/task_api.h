@@ -60,7 +60,7 @@ struct GemmArgs {
   const void* tmB;
 };
 
-struct PhaseDesc {
+struct alignas(16) PhaseDesc {
   int kind, ntasks, layout, epi;
   int tiles_m, i0, i1, i2;
   GemmArgs g;
@@ -71,6 +71,16 @@ struct PhaseDesc {
 
 struct Dep { int phase; int delta; };   // need done[phase] >= ntasks[phase] * (step + 1 + delta)
 
+// Everything the scheduler thread needs to place a ticket in a phase and to check that phase's dependencies, in one 64-byte
+// line: one memory round trip per phase change instead of a chain of dependent table look-ups.
+struct alignas(16) SchedRec {
+  int lo, hi;               // tickets [lo, hi) of a step belong to this phase
+  int ndeps;                // 0..4 dependencies held in dep[]; -1: more than four, use Job::deps
+  int pad;
+  int dep[12];              // per dependency: phase, step delta, task count of that phase
+};
+constexpr int CTRL_BYTES = 1024;   // control area at the end of every block's dynamic shared memory
+
 struct Job {
   int nph, tasks_per_step, nsteps, last_phase;
   const PhaseDesc* ph;      // [nph]
@@ -79,6 +89,7 @@ struct Job {
   const int* dep_off;       // [nph]
   const int* dep_cnt;       // [nph]
   const Dep* deps;
+  const SchedRec* rec;      // [nph]
   int* done;                // [nph] monotonically increasing over steps
   unsigned* ticket;         // next (step * tasks_per_step + task) to hand out
 };

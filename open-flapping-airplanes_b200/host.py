@@ -148,7 +148,9 @@ class Megakernel:
         for i in range(self.lib.ofa_num_phases(self.h)):
             name = C.create_string_buffer(64); kind, nt, busy = C.c_int(), C.c_int(), C.c_ulonglong()
             self._chk(self.lib.ofa_phase_info(self.h, i, name, 64, C.byref(kind), C.byref(nt), C.byref(busy)))
-            res.append({"name": name.value.decode(), "kind": kind.value, "ntasks": nt.value, "busy_ns": busy.value})
+            wait = C.c_ulonglong()
+            self._chk(self.lib.ofa_phase_wait_ns(self.h, i, C.byref(wait)))
+            res.append({"name": name.value.decode(), "kind": kind.value, "ntasks": nt.value, "busy_ns": busy.value, "wait_ns": wait.value})
         return res
 
     def block_busy_ns(self, nblocks=296):
