@@ -17,7 +17,7 @@ class Config(C.Structure):
         ("data_seed", C.c_ulonglong),
         ("infer_sms", C.c_int), ("reserved_sms", C.c_int), ("train_sms", C.c_int), ("use_decode", C.c_int),
         ("n_prompt", C.c_int), ("prompt", C.c_int * 32), ("answer_len", C.c_int), ("temperature", C.c_float), ("decode_seed", C.c_ulonglong),
-        ("decode_out_cap", C.c_int), ("dp_world", C.c_int), ("grad_bf16", C.c_int), ("ext_sync", C.c_int), ("bucket_bytes", C.c_int), ("adam_interleave", C.c_int), ("head_dx_splitk", C.c_int),
+        ("decode_out_cap", C.c_int), ("dp_world", C.c_int), ("grad_bf16", C.c_int), ("ext_sync", C.c_int), ("bucket_bytes", C.c_int), ("attn_legacy", C.c_int), ("adam_interleave", C.c_int), ("head_dx_splitk", C.c_int),
         ("gemm_nsub", C.c_int), ("timeout_s", C.c_double), ("device", C.c_int),
     ]
 

@@ -19,6 +19,7 @@
 #include "elementwise.cuh"
 #include "gemm_tc.cuh"
 #include "attn_mma.cuh"
+#include "attn_tc.cuh"
 #include "simt_f32.cuh"
 #include "decode.cuh"
 #include <type_traits>
@@ -30,7 +31,7 @@ template <class T> struct IsBf16 { static constexpr bool value = std::is_same<T,
 // ---------------------------------------------------------------------------------------------- one training task
 template <class T, int D, int DH>
 __device__ __forceinline__ void run_train_task(const Ctx& C, const PhaseDesc& d, int ph, int local, int step, unsigned char* smem,
-                                               gemm_tc::GemmPipe& gp) {
+                                               gemm_tc::GemmPipe& gp, attn_tc::AttnPipe& ap) {
   const ModelDims& md = C.md;
   switch (d.kind) {
     case TK_DATA:
@@ -50,7 +51,8 @@ __device__ __forceinline__ void run_train_task(const Ctx& C, const PhaseDesc& d,
       if constexpr (IsBf16<T>::value) {
         const int BH = md.B * md.H, QT = md.T / attn::QTILE;
         const int qt = QT - 1 - local / BH, bh = local % BH;      // heavy (late) query tiles first
-        attn::fwd_task((const bf16*)d.p[0], (bf16*)d.p[1], (float*)d.p[2], bh / md.H, bh % md.H, qt, md.T, md.H, smem);
+        if (d.p[6]) attn_tc::fwd_task((const attn_tc::Maps*)d.p[6], (bf16*)d.p[1], (float*)d.p[2], bh / md.H, bh % md.H, qt, md.T, md.H, smem, ap, gp.tmem_base, C.status, ph, local);
+        else attn::fwd_task((const bf16*)d.p[0], (bf16*)d.p[1], (float*)d.p[2], bh / md.H, bh % md.H, qt, md.T, md.H, smem);
       } else {
         f32::attn_fwd_task<DH>((const float*)d.p[0], (float*)d.p[1], (float*)d.p[2], local / md.H, local % md.H, md.T, md.H, smem);
       }
@@ -69,11 +71,13 @@ __device__ __forceinline__ void run_train_task(const Ctx& C, const PhaseDesc& d,
         const int BH = md.B * md.H, QT = md.T / attn::QTILE;
         if (local < BH * QT) {                                     // dK/dV: early key tiles see the most queries -> first
           const int kt = local / BH, bh = local % BH;
-          attn::bwd_dkdv_task((const bf16*)d.p[0], (const bf16*)d.p[1], (const float*)d.p[2], (const float*)d.p[3], (bf16*)d.p[4],
+          if (d.p[6]) attn_tc::bwd_dkdv_task((const attn_tc::Maps*)d.p[6], (const float*)d.p[2], (const float*)d.p[3], (bf16*)d.p[4], bh / md.H, bh % md.H, kt, md.T, md.H, smem, ap, gp.tmem_base, C.status, ph, local);
+          else attn::bwd_dkdv_task((const bf16*)d.p[0], (const bf16*)d.p[1], (const float*)d.p[2], (const float*)d.p[3], (bf16*)d.p[4],
                               bh / md.H, bh % md.H, kt, md.T, md.H, smem);
         } else {                                                   // dQ: late query tiles see the most keys -> first
           const int l2 = local - BH * QT, qt = QT - 1 - l2 / BH, bh = l2 % BH;
-          attn::bwd_dq_task((const bf16*)d.p[0], (const bf16*)d.p[1], (const float*)d.p[2], (const float*)d.p[3], (bf16*)d.p[4],
+          if (d.p[6]) attn_tc::bwd_dq_task((const attn_tc::Maps*)d.p[6], (const float*)d.p[2], (const float*)d.p[3], (bf16*)d.p[4], bh / md.H, bh % md.H, qt, md.T, md.H, smem, ap, gp.tmem_base, C.status, ph, local);
+          else attn::bwd_dq_task((const bf16*)d.p[0], (const bf16*)d.p[1], (const float*)d.p[2], (const float*)d.p[3], (bf16*)d.p[4],
                             bh / md.H, bh % md.H, qt, md.T, md.H, smem);
         }
       } else {
@@ -225,7 +229,8 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
   const unsigned total = (unsigned)J.nsteps * (unsigned)J.tasks_per_step;
   gemm_tc::GemmPipe gp; gp.stage_count[0] = gp.stage_count[1] = gp.tile_count[0] = gp.tile_count[1] = gp.tmem_base = 0;
   const bool use_tc = IsBf16<T>::value && job_id == 0;
-  if (use_tc) gemm_tc::block_init(gp, smem, C.status);
+  attn_tc::AttnPipe ap; ap.tasks = ap.stages = ap.stages2 = ap.a = ap.b = ap.done = 0;
+  if (use_tc) { attn_tc::block_init(ap, smem); gemm_tc::block_init(gp, smem, C.status); }
   // serving blocks: one mbarrier counts the bytes of the weight prefetch of the task they hold a ticket for
   const uint32_t fill_bar = smem_u32(ctrl + 96);
   uint32_t fills = 0;
@@ -311,7 +316,7 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
     }
     u64 t0 = 0;
     if (tid == 0) { t0 = gtimer(); t_sync += t0 - tl1; if (job_id == 1 && C.dp.trace && local == 0 && (ph == 0 || ph == 2)) C.dp.trace[16 + ph] = t0; }
-    if (job_id == 0) run_train_task<T, D, DH>(C, d, ph, local, step, smem, gp);
+    if (job_id == 0) run_train_task<T, D, DH>(C, d, ph, local, step, smem, gp, ap);
     else run_decode_task<T, D, DH>(C, d, local, smem, fill_bar, fills & 1u);
     if (filled) fills++;
     __syncthreads();

@@ -99,6 +99,18 @@ struct Arena {   // device allocations owned by one context / one ofa_run_phases
   void free_all() { for (void* p : ptrs) cudaFree(p); ptrs.clear(); }
 };
 
+// TMA descriptors of one layer's attention operands (qkv [N, 3D] and, for the backward tasks, dO [N, D]) in device memory
+const void* make_attn_maps(Arena& ar, const void* qkv, const void* dO, int N, int D, std::string& err) {
+  attn_tc::Maps* dm = ar.alloc<attn_tc::Maps>(1, false);
+  if (ar.dry || !dm) return dm;
+  attn_tc::Maps hm; memset(&hm, 0, sizeof hm);
+  bool ok = encode_map(&hm.qkv128, qkv, 3 * D, N, 3 * D, 64, 128) && encode_map(&hm.qkv64, qkv, 3 * D, N, 3 * D, 64, 64);
+  if (dO) ok = ok && encode_map(&hm.dO128, dO, D, N, D, 64, 128) && encode_map(&hm.dO64, dO, D, N, D, 64, 64);
+  if (!ok) { err = "cuTensorMapEncodeTiled failed (attention)"; return nullptr; }
+  ar.h2d(dm, &hm, sizeof hm);
+  return dm;
+}
+
 // Validates a GEMM description for the tensor-core path and fills task counts + TMA descriptors (device memory).
 bool prepare_gemm_bf16(PhaseDesc& d, Arena& ar, int nsub_cfg, int nblocks, std::string& err) {
   GemmArgs& g = d.g;
@@ -355,7 +367,9 @@ bool build_train_graph(ofa_ctx* c) {
     { PhaseDesc d = mk(TK_LN_FWD, rows16); d.p[0] = ln1[l]; d.p[1] = mean1[l]; d.p[2] = rstd1[l]; d.p[3] = xs[l]; d.p[4] = Wact + lay.g1[l];
       addp(s + "ln1", d, {prev}, {opt_layer(l)}); }
     addp(s + "qkv", mkgemm(GL_NN, GE_STORE, ln1[l], D, Wact + lay.wqkv[l], 3 * D, qkv[l], 3 * D, nullptr, 0, N, 3 * D, D, 0), {s + "ln1"}, {});
-    { PhaseDesc d = mk(TK_ATT_FWD, attn_fwd_tasks); d.p[0] = qkv[l]; d.p[1] = att[l]; d.p[2] = lse[l]; addp(s + "attn", d, {s + "qkv"}, {}); }
+    { PhaseDesc d = mk(TK_ATT_FWD, attn_fwd_tasks); d.p[0] = qkv[l]; d.p[1] = att[l]; d.p[2] = lse[l];
+      if (bf && !cfg.attn_legacy) { std::string e; d.p[6] = const_cast<void*>(make_attn_maps(c->ar, qkv[l], nullptr, N, D, e)); if (!d.p[6]) { ok = false; err = e; } }
+      addp(s + "attn", d, {s + "qkv"}, {}); }
     addp(s + "wo+res", mkgemm(GL_NN, GE_RES, att[l], D, Wact + lay.wo[l], D, hb[l], D, xs[l], D, N, D, D, 0), {s + "attn"}, {});
     { PhaseDesc d = mk(TK_LN_FWD, rows16); d.p[0] = ln2[l]; d.p[1] = mean2[l]; d.p[2] = rstd2[l]; d.p[3] = hb[l]; d.p[4] = Wact + lay.g2[l];
       addp(s + "ln2", d, {s + "wo+res"}, {}); }
@@ -478,6 +492,7 @@ bool build_train_graph(ofa_ctx* c) {
       addp(s + "dWo", mkgemm(GL_TN, wepi, att[l], D, dh[l], D, G(lay.wo[l]), D, nullptr, 0, D, D, N, 0), {s + "ln2 bwd"}, {});
       { PhaseDesc d = mk(TK_ATT_PREP, bf ? attn_fwd_tasks : 1); d.p[0] = att[l]; d.p[1] = dob[l]; d.p[2] = Dr[l]; addp(s + "attn prep", d, {s + "dO"}, {}); }
       { PhaseDesc d = mk(TK_ATT_BWD, attn_bwd_tasks); d.p[0] = qkv[l]; d.p[1] = dob[l]; d.p[2] = lse[l]; d.p[3] = Dr[l]; d.p[4] = dqkv[l]; d.p[5] = att[l];
+        if (bf && !cfg.attn_legacy) { std::string e; d.p[6] = const_cast<void*>(make_attn_maps(c->ar, qkv[l], dob[l], N, D, e)); if (!d.p[6]) { ok = false; err = e; } }
         addp(s + "attn bwd", d, {s + "attn prep"}, {}); }
       addp(s + "dln1", mkgemm(GL_NT, GE_STORE, dqkv[l], 3 * D, Wact + lay.wqkv[l], 3 * D, dln1[l], D, nullptr, 0, N, D, 3 * D, 0), {s + "attn bwd"}, {});
       addp(s + "dWqkv", mkgemm(GL_TN, wepi, ln1[l], D, dqkv[l], 3 * D, G(lay.wqkv[l]), 3 * D, nullptr, 0, D, 3 * D, N, 0), {s + "attn bwd"}, {});
@@ -1070,9 +1085,13 @@ extern "C" int ofa_run_phases(int dtype, const ofa_dims* dims, const ofa_phase* 
         break;
       case TK_EMBED: case TK_LN_FWD: case TK_LN_BWD: d.ntasks = rows16; break;
       case TK_LN_DG: d.ntasks = (m.D + NTHR - 1) / NTHR; break;
-      case TK_ATT_FWD: d.ntasks = bf ? BH * (m.T / attn::QTILE) : BH; break;
+      case TK_ATT_FWD: d.ntasks = bf ? BH * (m.T / attn::QTILE) : BH;
+        if (bf && !s.i0) { d.p[6] = const_cast<void*>(make_attn_maps(ar, s.p[0], nullptr, m.N, m.D, err)); if (!d.p[6]) { ar.free_all(); return fail(nullptr, OFA_CUDA_ERROR, err); } }   // i0 = 1: mma.sync tasks
+        break;
       case TK_ATT_PREP: d.ntasks = bf ? BH * (m.T / attn::QTILE) : 1; break;
-      case TK_ATT_BWD: d.ntasks = bf ? 2 * BH * (m.T / attn::QTILE) : BH; break;
+      case TK_ATT_BWD: d.ntasks = bf ? 2 * BH * (m.T / attn::QTILE) : BH;
+        if (bf && !s.i0) { d.p[6] = const_cast<void*>(make_attn_maps(ar, s.p[0], s.p[1], m.N, m.D, err)); if (!d.p[6]) { ar.free_all(); return fail(nullptr, OFA_CUDA_ERROR, err); } }
+        break;
       case TK_CE: d.ntasks = (m.N + ew::CE_ROWS - 1) / ew::CE_ROWS;
         d.i0 = (int)(std::min<size_t>((size_t)((bf ? gemm_tc::BAR_OFFSET : smem - CTRL_BYTES) - 64), (size_t)m.V * (bf ? 2 : 4)) / 16 * 16); break;
       case TK_CE_MEAN: case TK_BARRIER: d.ntasks = 1; break;

@@ -68,6 +68,9 @@ def run_gemm(ofa, name, repeats, nsub):
     return {"kernel": name, "shape": [Mm, Nn, Kk], "ms": ms, "tflops": flop / ms / 1e9, "bound": "tensor", "algorithmic_bytes": bytes_set, "buffer_sets": nsets}
 
 
+ATTN_LEGACY = 0      # --attn-legacy: time the mma.sync attention tasks instead of the tcgen05 ones
+
+
 def run_attn(ofa, which, repeats):
     K = ofa.capi
     rng = np.random.default_rng(1)
@@ -79,10 +82,10 @@ def run_attn(ofa, which, repeats):
         o = ofa.DeviceBuffer((N, D), "bf16"); lse = ofa.DeviceBuffer((B, H, T), np.float32); Dr = ofa.DeviceBuffer((B, H, T), np.float32); dqkv = ofa.DeviceBuffer((N, 3 * D), "bf16")
         keep += [qkv, dO, o, lse, Dr, dqkv]
         if which == "attn_fwd":
-            phases.append(ofa.phase(K.TK_ATT_FWD, [qkv, o, lse]))
+            phases.append(ofa.phase(K.TK_ATT_FWD, [qkv, o, lse], i0=ATTN_LEGACY))
         else:
             ofa.run_phases(K.DTYPE_BF16, DIMS, [ofa.phase(K.TK_ATT_FWD, [qkv, o, lse])])
-            phases += [ofa.phase(K.TK_ATT_PREP, [o, dO, Dr]), ofa.phase(K.TK_ATT_BWD, [qkv, dO, lse, Dr, dqkv, o])]
+            phases += [ofa.phase(K.TK_ATT_PREP, [o, dO, Dr]), ofa.phase(K.TK_ATT_BWD, [qkv, dO, lse, Dr, dqkv, o], i0=ATTN_LEGACY)]
     ms = ofa.run_phases(K.DTYPE_BF16, DIMS, phases, repeats=repeats) / (repeats * nsets)
     fwd_flop = 4.0 * B * H * T * T * 64 / 2
     flop = fwd_flop if which == "attn_fwd" else 2.5 * fwd_flop
@@ -184,8 +187,11 @@ def main():
     ap.add_argument("--only", default="")
     ap.add_argument("--repeats", type=int, default=5)
     ap.add_argument("--nsub", type=int, default=0)
+    ap.add_argument("--attn-legacy", action="store_true")
     ap.add_argument("--list", action="store_true")
     a = ap.parse_args()
+    global ATTN_LEGACY
+    ATTN_LEGACY = 1 if a.attn_legacy else 0
     names = list(GEMMS) + OTHERS
     if a.list:
         print("\n".join(names)); return

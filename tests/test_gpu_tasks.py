@@ -218,8 +218,9 @@ def test_gemm_fp32_simt(ofa, K, oracle, layout, epi, M, N, Kd):
         assert relmax(dAux.download(), aux_ref) <= 2e-5
 
 
+@pytest.mark.parametrize("legacy", [0, 1])            # 0: tcgen05 tasks (tensor-memory accumulators), 1: mma.sync tasks
 @pytest.mark.parametrize("B,T", [(2, 256), (1, 1024), (3, 128)])
-def test_attention_bf16_forward_backward(ofa, K, oracle, B, T):
+def test_attention_bf16_forward_backward(ofa, K, oracle, B, T, legacy):
     H, dh = 12, 64
     D = H * dh
     dims = dict(DIMS_S, ctx_len=T, batch=B)
@@ -229,8 +230,8 @@ def test_attention_bf16_forward_backward(ofa, K, oracle, B, T):
     d_qkv = ofa.DeviceBuffer.from_host(qkv.numpy(), "bf16"); d_dO = ofa.DeviceBuffer.from_host(dO.numpy(), "bf16")
     d_o = ofa.DeviceBuffer((N, D), "bf16"); d_lse = ofa.DeviceBuffer((B, H, T), np.float32); d_Dr = ofa.DeviceBuffer((B, H, T), np.float32)
     d_dqkv = ofa.DeviceBuffer((N, 3 * D), "bf16")
-    phases = [ofa.phase(K.TK_ATT_FWD, [d_qkv, d_o, d_lse]), ofa.phase(K.TK_ATT_PREP, [d_o, d_dO, d_Dr]),
-              ofa.phase(K.TK_ATT_BWD, [d_qkv, d_dO, d_lse, d_Dr, d_dqkv, d_o])]
+    phases = [ofa.phase(K.TK_ATT_FWD, [d_qkv, d_o, d_lse], i0=legacy), ofa.phase(K.TK_ATT_PREP, [d_o, d_dO, d_Dr]),
+              ofa.phase(K.TK_ATT_BWD, [d_qkv, d_dO, d_lse, d_Dr, d_dqkv, d_o], i0=legacy)]
     ofa.run_phases(K.DTYPE_BF16, dims, phases)
     o_ref, lse_ref = oracle.attention_ref(qkv, B, T, H, dh)
     assert relmax(d_o.download(), o_ref) <= 2e-2
