@@ -8,8 +8,11 @@
 //
 // Every task has the same three roles and the same step:
 //   producer (warp 0, one thread)   TMA: the task's own 128-row tiles once, then per step two 64-row partner tiles
-//   issuer   (warp 1, one thread)   group A: scores (and dP) of the step into tensor memory;   group B: the products that
-//                                   consume what the softmax threads wrote to shared memory
+//   issuers  (warps 1 and 2, one thread each)   warp 1, group A: scores (and dP) of the step into tensor memory, as far
+//                                   ahead of the softmax threads as the buffers allow;  warp 2, group B: the products that
+//                                   consume what the softmax threads wrote to shared memory. Two threads because one thread
+//                                   issues a tcgen05.mma only every ~96 cycles (measured) and because the two groups wait
+//                                   for different things
 //   softmax  (warps 4-7)            thread = row = tensor-memory lane: reads group A's result with tcgen05.ld, writes bf16
 //                                   operands for group B into a SWIZZLE_128B K-major tile, hands both back with mbarriers
 //   forward  step = 64 keys:    A: S = Q K_j^T            softmax: online max/sum, P_j        B: O += P_j V_j
@@ -153,28 +156,29 @@ __device__ __noinline__ void fwd_task(const Maps* mp, bf16* o, float* lse, int b
       if (aborted(st)) drain(base, B_STFULL, ap.stages, sc, NST);
     }
   } else if (warp == 1) {
-    if (lane == 0) {                                                           // ---- issuer
+    if (lane == 0) {                                                           // ---- issuer of the scores: up to two steps ahead of the softmax threads
       bool ok = wait_or_abort(bar(base, B_QFULL), ap.tasks & 1, st, ST_MBAR_FULL_TIMEOUT, phase_id, task, 1000);
-      for (int j = 0; j <= n && ok; j++) {
-        if (j < n) {                                                           // S_j (issued one step ahead of the product that uses P_{j-1})
-          const uint32_t sc = ap.stages + j, c = ap.a + j; const int s = sc % NST;
-          ok = wait_or_abort(bar(base, B_STFULL + s), (sc / NST) & 1, st, ST_MBAR_FULL_TIMEOUT, phase_id, task, j);
-          if (ok && j >= 2) ok = wait_or_abort(bar(base, B_AFREE + (c & 1)), ((c - 2) >> 1) & 1, st, ST_MBAR_ACC_TIMEOUT, phase_id, task, j);
-          if (!ok) break;
-          tc_fence_after();
-          mma_64(tmem + (c & 1) * 64, sQ, sSt + s * 16384, false, false);
-          umma_commit(bar(base, B_AFULL + (c & 1)));
-        }
-        if (j > 0) {                                                           // O += P_{j-1} V_{j-1}
-          const int i = j - 1;
-          const uint32_t sc = ap.stages + i, c = ap.a + i, cb = ap.b + i; const int s = sc % NST;
-          ok = wait_or_abort(bar(base, B_WFULL + (c & 1)), (c >> 1) & 1, st, ST_MBAR_FULL_TIMEOUT, phase_id, task, 2000 + i);
-          if (!ok) break;
-          tc_fence_after();
-          mma_64(tmem + 128, sP + (c & 1) * 16384, sSt + s * 16384 + 8192, true, i > 0);
-          umma_commit(bar(base, B_STEMPTY + s));
-          umma_commit(bar(base, B_BFULL + (cb & 1)));
-        }
+      for (int j = 0; j < n && ok; j++) {
+        const uint32_t sc = ap.stages + j, c = ap.a + j; const int s = sc % NST;
+        ok = wait_or_abort(bar(base, B_STFULL + s), (sc / NST) & 1, st, ST_MBAR_FULL_TIMEOUT, phase_id, task, j);
+        if (ok && j >= 2) ok = wait_or_abort(bar(base, B_AFREE + (c & 1)), ((c - 2) >> 1) & 1, st, ST_MBAR_ACC_TIMEOUT, phase_id, task, j);
+        if (!ok) break;
+        tc_fence_after();
+        mma_64(tmem + (c & 1) * 64, sQ, sSt + s * 16384, false, false);
+        umma_commit(bar(base, B_AFULL + (c & 1)));
+      }
+    }
+  } else if (warp == 2) {
+    if (lane == 0) {                                                           // ---- issuer of the products: follows the softmax threads
+      bool ok = true;
+      for (int i = 0; i < n && ok; i++) {                                      // O += P_i V_i
+        const uint32_t sc = ap.stages + i, c = ap.a + i, cb = ap.b + i; const int s = sc % NST;
+        ok = wait_or_abort(bar(base, B_WFULL + (c & 1)), (c >> 1) & 1, st, ST_MBAR_FULL_TIMEOUT, phase_id, task, 2000 + i);
+        if (!ok) break;
+        tc_fence_after();
+        mma_64(tmem + 128, sP + (c & 1) * 16384, sSt + s * 16384 + 8192, true, i > 0);
+        umma_commit(bar(base, B_STEMPTY + s));
+        umma_commit(bar(base, B_BFULL + (cb & 1)));
       }
     }
   } else if (warp >= 4) {                                                      // ---- softmax threads: thread = query row
@@ -323,7 +327,7 @@ __device__ __noinline__ void bwd_dkdv_task(const Maps* mp, const float* lse, con
       if (aborted(st)) drain(base, B_ST2FULL, st0, sc, NST);
     }
   } else if (warp == 1) {
-    if (lane == 0) {                                                           // ---- issuer
+    if (lane == 0) {                                                           // ---- issuer of the scores: runs one step ahead of the softmax threads
       bool ok = wait_or_abort(bar(base, B_QFULL), ap.tasks & 1, st, ST_MBAR_FULL_TIMEOUT, phase_id, task, 1000);
       for (int i = 0; i < n && ok; i++) {
         const uint32_t sc = st0 + i, c = ap.a + i; const int s = sc % NST;
@@ -334,6 +338,13 @@ __device__ __noinline__ void bwd_dkdv_task(const Maps* mp, const float* lse, con
         mma_64(tmem, sK, sSt + s * 16384, false, false);                       // S^T  = K Q_i^T
         mma_64(tmem + 64, sV, sSt + s * 16384 + 8192, false, false);           // dP^T = V dO_i^T
         umma_commit(bar(base, B_AFULL + (c & 1)));
+      }
+    }
+  } else if (warp == 2) {
+    if (lane == 0) {                                                           // ---- issuer of the products: follows the softmax threads
+      bool ok = true;
+      for (int i = 0; i < n && ok; i++) {
+        const uint32_t sc = st0 + i, c = ap.a + i; const int s = sc % NST;
         ok = wait_or_abort(bar(base, B_WFULL + (c & 1)), (c >> 1) & 1, st, ST_MBAR_FULL_TIMEOUT, phase_id, task, 2000 + i);
         if (!ok) break;
         tc_fence_after();
@@ -356,12 +367,17 @@ __device__ __noinline__ void bwd_dkdv_task(const Maps* mp, const float* lse, con
       tc_fence_after();
       const float* sL = reinterpret_cast<const float*>(smem + gemm_tc::PIPE_BYTES + s * 512); const float* sD = sL + 64;
       const bool need_mask = __any_sync(0xffffffffu, qi0 < kg);                 // warp-uniform: only blocks on the diagonal
+      uint32_t pp[2][16], pd[2][16];
 #pragma unroll
       for (int hf = 0; hf < 2; hf++) {
-        uint32_t rs[32], rd[32], pp[16], pd[16];
+        uint32_t rs[32], rd[32];
         tmem_ld32_nw(tl + hf * 32, rs);
         tmem_ld32_nw(tl + 64 + hf * 32, rd);
         tmem_ld_wait();
+        if (hf == 1) {                                                         // everything of this step is in registers: the next scores may overwrite it
+          tc_fence_before();
+          warp_arrive(bar(base, B_AFREE + (c & 1)));
+        }
         if (need_mask) {                                                       // a masked score becomes -inf: 2^-inf = 0 for P, and dS = 0 * (..) = 0
 #pragma unroll
           for (int x = 0; x < 32; x++) if (kg > qi0 + hf * 32 + x) rs[x] = 0xff800000u;
@@ -371,14 +387,18 @@ __device__ __noinline__ void bwd_dkdv_task(const Maps* mp, const float* lse, con
           const int ql = hf * 32 + x;
           const float p0 = ex2(fmaf(__uint_as_float(rs[x]), SCALE_LOG2, -sL[ql] * LOG2E)), p1 = ex2(fmaf(__uint_as_float(rs[x + 1]), SCALE_LOG2, -sL[ql + 1] * LOG2E));
           const float d0 = p0 * (__uint_as_float(rd[x]) - sD[ql]), d1 = p1 * (__uint_as_float(rd[x + 1]) - sD[ql + 1]);
-          pp[x >> 1] = pack2(p0, p1); pd[x >> 1] = pack2(d0, d1);
+          pp[hf][x >> 1] = pack2(p0, p1); pd[hf][x >> 1] = pack2(d0, d1);
         }
-        store_chunks(smem + 65536, r, hf * 4, pp);
-        store_chunks(smem + 81920, r, hf * 4, pd);
       }
-      tc_fence_before();
+      if (i >= 1) {                                                            // the previous step's products read the tiles about to be rewritten
+        const uint32_t scp = sc - 1;
+        ok = mbar_wait(bar(base, B_ST2EMPTY + (int)(scp % NST)), (scp / NST) & 1, st);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+      }
+#pragma unroll
+      for (int hf = 0; hf < 2; hf++) { store_chunks(smem + 65536, r, hf * 4, pp[hf]); store_chunks(smem + 81920, r, hf * 4, pd[hf]); }
       fence_async_smem();
-      warp_arrive(bar(base, B_AFREE + (c & 1)));
       warp_arrive(bar(base, B_WFULL + (c & 1)));
     }
     if (ok) { ok = mbar_wait(bar(base, B_DONE), ap.done & 1, st); ok = __all_sync(0xffffffffu, ok); }
@@ -438,7 +458,7 @@ __device__ __noinline__ void bwd_dq_task(const Maps* mp, const float* lse, const
       if (aborted(st)) drain(base, B_STFULL, ap.stages, sc, NST);
     }
   } else if (warp == 1) {
-    if (lane == 0) {                                                           // ---- issuer
+    if (lane == 0) {                                                           // ---- issuer of the scores: runs one step ahead of the softmax threads
       bool ok = wait_or_abort(bar(base, B_QFULL), ap.tasks & 1, st, ST_MBAR_FULL_TIMEOUT, phase_id, task, 1000);
       for (int j = 0; j < n && ok; j++) {
         const uint32_t sc = ap.stages + j, c = ap.a + j; const int s = sc % NST;
@@ -449,6 +469,13 @@ __device__ __noinline__ void bwd_dq_task(const Maps* mp, const float* lse, const
         mma_64(tmem, sQ, sSt + s * 16384, false, false);                       // S  = Q K_j^T
         mma_64(tmem + 64, sdO, sSt + s * 16384 + 8192, false, false);          // dP = dO V_j^T
         umma_commit(bar(base, B_AFULL + (c & 1)));
+      }
+    }
+  } else if (warp == 2) {
+    if (lane == 0) {                                                           // ---- issuer of the products: follows the softmax threads
+      bool ok = true;
+      for (int j = 0; j < n && ok; j++) {
+        const uint32_t sc = ap.stages + j, c = ap.a + j; const int s = sc % NST;
         ok = wait_or_abort(bar(base, B_WFULL + (c & 1)), (c >> 1) & 1, st, ST_MBAR_FULL_TIMEOUT, phase_id, task, 2000 + j);
         if (!ok) break;
         tc_fence_after();
@@ -470,12 +497,17 @@ __device__ __noinline__ void bwd_dq_task(const Maps* mp, const float* lse, const
       if (!ok) break;
       tc_fence_after();
       const bool need_mask = __any_sync(0xffffffffu, k0 + KTILE - 1 > qg);      // warp-uniform: only blocks on the diagonal
+      uint32_t pd[2][16];
 #pragma unroll
       for (int hf = 0; hf < 2; hf++) {
-        uint32_t rs[32], rd[32], pd[16];
+        uint32_t rs[32], rd[32];
         tmem_ld32_nw(tl + hf * 32, rs);
         tmem_ld32_nw(tl + 64 + hf * 32, rd);
         tmem_ld_wait();
+        if (hf == 1) {                                                         // everything of this step is in registers: the next scores may overwrite it
+          tc_fence_before();
+          warp_arrive(bar(base, B_AFREE + (c & 1)));
+        }
         if (need_mask) {
 #pragma unroll
           for (int x = 0; x < 32; x++) if (k0 + hf * 32 + x > qg) rs[x] = 0xff800000u;
@@ -483,13 +515,18 @@ __device__ __noinline__ void bwd_dq_task(const Maps* mp, const float* lse, const
 #pragma unroll
         for (int x = 0; x < 32; x += 2) {
           const float p0 = ex2(fmaf(__uint_as_float(rs[x]), SCALE_LOG2, -lse2)), p1 = ex2(fmaf(__uint_as_float(rs[x + 1]), SCALE_LOG2, -lse2));
-          pd[x >> 1] = pack2(p0 * (__uint_as_float(rd[x]) - dr), p1 * (__uint_as_float(rd[x + 1]) - dr));
+          pd[hf][x >> 1] = pack2(p0 * (__uint_as_float(rd[x]) - dr), p1 * (__uint_as_float(rd[x + 1]) - dr));
         }
-        store_chunks(smem + 81920, r, hf * 4, pd);
       }
-      tc_fence_before();
+      if (j >= 1) {                                                            // the previous step's product read the tile about to be rewritten
+        const uint32_t scp = ap.stages + j - 1;
+        ok = mbar_wait(bar(base, B_STEMPTY + (int)(scp % NST)), (scp / NST) & 1, st);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+      }
+      store_chunks(smem + 81920, r, 0, pd[0]);
+      store_chunks(smem + 81920, r, 4, pd[1]);
       fence_async_smem();
-      warp_arrive(bar(base, B_AFREE + (c & 1)));
       warp_arrive(bar(base, B_WFULL + (c & 1)));
     }
     if (ok) { ok = mbar_wait(bar(base, B_DONE), ap.done & 1, st); ok = __all_sync(0xffffffffu, ok); }
