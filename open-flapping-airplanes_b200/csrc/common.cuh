@@ -149,8 +149,11 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait: true when the phase with `parity` completed; false when the deadline passed or the grid is aborting.
+// The common case - the phase is already complete or completes within the first probe - must stay a handful of
+// instructions in the caller: with the polling loops inlined, a wait on a completed barrier measured 174 cycles instead of
+// the 14 of one mbarrier.try_wait, on every pipeline stage of every tile.
 constexpr u64 MBAR_TIMEOUT_NS = 2000000000ull;   // 2 s: far beyond any legitimate wait inside one tile
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const DevStatus* st) {
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, const DevStatus* st) {
 #pragma unroll 1
   for (int i = 0; i < 128; i++) if (mbar_try(bar, parity)) return true;
   const u64 t0 = gtimer();
@@ -158,9 +161,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const D
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 64; i++) if (mbar_try(bar, parity)) return true;
-    if (aborted(st)) return false;
+    if (st && aborted(st)) return false;
     if (gtimer() - t0 > MBAR_TIMEOUT_NS) return false;
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const DevStatus* st) {
+  if (mbar_try(bar, parity)) return true;
+  if (mbar_try(bar, parity)) return true;      // a try_wait blocks for a while by itself: the second probe catches most short waits
+  return mbar_wait_slow(bar, parity, st);
 }
 
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
