@@ -264,6 +264,75 @@ __device__ __forceinline__ void ce_task(int task, T* logits, const int* targets,
   }
 }
 
+// The same task for bf16 rows that fit the cache entirely: the row is brought into shared memory by bulk copies (the copy
+// engine streams it without occupying the threads or their registers; with the loop of 16-byte loads above a thread had one
+// or two loads in flight and the phase ran at a third of the HBM rate), then both passes read shared memory. The arithmetic
+// and its order are those of ce_task. `bar` is a block-private mbarrier, `uses` its running use count (advanced here).
+__device__ __forceinline__ void ce_task_bulk(int task, bf16* logits, const int* targets, float* loss, int N, int V, float inv_n,
+                                             unsigned char* smem, uint32_t bar, uint32_t& uses, const DevStatus* st) {
+  constexpr float L2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
+  float* red = reinterpret_cast<float*>(smem);
+  bf16* cache = reinterpret_cast<bf16*>(smem + 64);
+  const uint32_t cache_addr = smem_u32(cache);
+  const int t = threadIdx.x;
+  const int nvec = V / 8;
+  const uint32_t row_bytes = (uint32_t)V * 2u;
+  const uint32_t use0 = uses;
+  uses += CE_ROWS;                                     // every thread, whatever happens below
+  for (int rr = 0; rr < CE_ROWS; rr++) {
+    const int r = task * CE_ROWS + rr;
+    const uint32_t parity = (use0 + rr) & 1u;
+    if (r >= N) { if (t == 0) mbar_arrive(bar); continue; }          // keep the barrier's phase count in step with `uses`
+    bf16* row = logits + (size_t)r * V;
+    if (t == 0) {
+      fence_proxy_async();   // the row was written by a GEMM epilogue with ordinary stores; the cache was last read by ordinary loads
+      mbar_expect_tx(bar, row_bytes);
+      for (uint32_t off = 0; off < row_bytes; off += 32768u) {
+        const uint32_t nb = row_bytes - off < 32768u ? row_bytes - off : 32768u;
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(cache_addr + off), "l"(reinterpret_cast<const char*>(row) + off), "r"(nb), "r"(bar) : "memory");
+      }
+    }
+    const int tgt = targets[r];
+    bool ok = true;
+    if (t == 0) {                                      // one thread polls; the block barrier below hands the result (and the data) to the rest
+      ok = mbar_wait(bar, parity, st);
+      if (!ok) { for (int spin = 0; spin < 100000 && !mbar_try(bar, parity); spin++) {} }   // leaving: give the copy a bounded chance to land
+    }
+    if (__syncthreads_or(!ok)) return;
+    float m = -INFINITY, s = 0.f;
+    for (int v = t; v < nvec; v += NTHR) {
+      float f[8];
+      unpack8(*reinterpret_cast<const uint4*>(cache + (size_t)v * 8), f);
+      float cm = f[0];
+#pragma unroll
+      for (int k = 1; k < 8; k++) cm = fmaxf(cm, f[k]);
+      cm *= L2E;
+      if (cm > m) { s *= exp2f(m - cm); m = cm; }
+#pragma unroll
+      for (int k = 0; k < 8; k++) s += exp2f(fmaf(f[k], L2E, -m));
+    }
+    float lt = 0.f;
+    if (t == 0) lt = to_f(cache[tgt]);
+    const float M = block_max(m, red);
+    const float S = block_sum(s * exp2f(m - M), red);
+    if (t == 0) loss[r] = M * LN2 + logf(S) - lt;
+    const float invS = 1.f / S;
+    for (int v = t; v < nvec; v += NTHR) {
+      float f[8];
+      unpack8(*reinterpret_cast<const uint4*>(cache + (size_t)v * 8), f);
+#pragma unroll
+      for (int k = 0; k < 8; k++) {
+        float p = exp2f(fmaf(f[k], L2E, -M)) * invS;
+        if (v * 8 + k == tgt) p -= 1.f;
+        f[k] = p * inv_n;
+      }
+      *reinterpret_cast<uint4*>(row + (size_t)v * 8) = pack8(f);
+    }
+    __syncthreads();   // cache and scratch are reused by the next row
+  }
+}
+
 // mean_loss[0] = (sum_r loss[r]) / N, fixed order. One task.
 __device__ __forceinline__ float ce_mean_task(float* mean_loss, const float* loss, int N, unsigned char* smem) {
   float s = 0.f;
@@ -396,7 +465,7 @@ __device__ __forceinline__ void adamw_task(int task, float* W, const GT* G, floa
     while (lo < hi) { const int mid = (lo + hi) >> 1; if ((size_t)nodecay[mid].y <= cs) lo = mid + 1; else hi = mid; }
   }
   const bool any_nd = lo < n_nodecay && (size_t)nodecay[lo].x < ce;
-#pragma unroll 2
+#pragma unroll 4
   for (size_t i = cs + (size_t)threadIdx.x * 4; i < ce; i += NTHR * 4) {
     float w[4], g[4], m[4], v[4];
     ld4(W + i, w); ld4(G + i, g); ld4(M + i, m); ld4(Vv + i, v);

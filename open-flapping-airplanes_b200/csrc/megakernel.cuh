@@ -31,7 +31,7 @@ template <class T> struct IsBf16 { static constexpr bool value = std::is_same<T,
 // ---------------------------------------------------------------------------------------------- one training task
 template <class T, int D, int DH>
 __device__ __forceinline__ void run_train_task(const Ctx& C, const PhaseDesc& d, int ph, int local, int step, unsigned char* smem,
-                                               gemm_tc::GemmPipe& gp, attn_tc::AttnPipe& ap) {
+                                               gemm_tc::GemmPipe& gp, attn_tc::AttnPipe& ap, uint32_t& bulk_uses) {
   const ModelDims& md = C.md;
   switch (d.kind) {
     case TK_DATA:
@@ -87,6 +87,13 @@ __device__ __forceinline__ void run_train_task(const Ctx& C, const PhaseDesc& d,
       break;
     }
     case TK_CE:
+      if constexpr (IsBf16<T>::value) {
+        if ((size_t)md.V * 2 <= (size_t)d.i0 && md.V % 8 == 0) {
+          ew::ce_task_bulk(local, (bf16*)d.p[0], (const int*)d.p[1], (float*)d.p[2], md.N, md.V, 1.0f / (float)md.N, smem,
+                           smem_u32(smem + C.smem_bytes - CTRL_BYTES + 104), bulk_uses, C.status);
+          break;
+        }
+      }
       ew::ce_task<T>(local, (T*)d.p[0], (const int*)d.p[1], (float*)d.p[2], md.N, md.V, 1.0f / (float)md.N, smem, d.i0);
       break;
     case TK_CE_MEAN: {
@@ -230,7 +237,8 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
   gemm_tc::GemmPipe gp; gp.stage_count[0] = gp.stage_count[1] = gp.tile_count[0] = gp.tile_count[1] = gp.tmem_base = 0;
   const bool use_tc = IsBf16<T>::value && job_id == 0;
   attn_tc::AttnPipe ap; ap.tasks = ap.stages = ap.stages2 = ap.a = ap.b = ap.done = 0;
-  if (use_tc) { attn_tc::block_init(ap, smem); gemm_tc::block_init(gp, smem, C.status); }
+  uint32_t bulk_uses = 0;                            // uses of the block's bulk-copy barrier (control area byte 104)
+  if (use_tc) { if (tid == 0) mbar_init(smem_u32(ctrl + 104), 1); attn_tc::block_init(ap, smem); gemm_tc::block_init(gp, smem, C.status); }
   // serving blocks: one mbarrier counts the bytes of the weight prefetch of the task they hold a ticket for
   const uint32_t fill_bar = smem_u32(ctrl + 96);
   uint32_t fills = 0;
@@ -316,7 +324,7 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
     }
     u64 t0 = 0;
     if (tid == 0) { t0 = gtimer(); t_sync += t0 - tl1; if (job_id == 1 && C.dp.trace && local == 0 && (ph == 0 || ph == 2)) C.dp.trace[16 + ph] = t0; }
-    if (job_id == 0) run_train_task<T, D, DH>(C, d, ph, local, step, smem, gp, ap);
+    if (job_id == 0) run_train_task<T, D, DH>(C, d, ph, local, step, smem, gp, ap, bulk_uses);
     else run_decode_task<T, D, DH>(C, d, local, smem, fill_bar, fills & 1u);
     if (filled) fills++;
     __syncthreads();
