@@ -32,6 +32,9 @@ V, D, L, H, T, B = 50304, 768, 12, 12, 1024, 4
 TOKENS_PER_STEP = B * T
 P_MM = L * 12 * D * D + V * D                                   # matmul parameters
 FLOP_PER_STEP = 6 * TOKENS_PER_STEP * P_MM + L * 3.5 * (4 * B * H * T * T * (D // H) / 2)   # 3.307e12, causal attention counted once
+# dram__bytes_read.sum + dram__bytes_write.sum of the megakernel per step, split workload on one GPU (ncu capture of a 2-step launch,
+# concurrent decoder included; the profiles folder holds the command and the raw figures)
+SPLIT_DRAM_BYTES_PER_STEP = 19.3e9
 
 
 def measured_peaks():
@@ -261,7 +264,7 @@ def main():
             "e2e": {"value": world * TOKENS_PER_STEP * K / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": int(window.nbytes / K + starts.nbytes / K), "d2h_bytes_per_step": 4},
             "gpu_launches": 1,
             "roofline": {"bound": "tensor", "achieved": achieved_tf, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved_tf / peak_tf,
-                         "traffic": None, "peak_source": f"{how} bf16_tflops_sustained x {sms_used}/148 SMs", "flop_per_step": FLOP_PER_STEP},
+                         "traffic": SPLIT_DRAM_BYTES_PER_STEP if (args.workload == "split" and world == 1) else None, "peak_source": f"{how} bf16_tflops_sustained x {sms_used}/148 SMs", "flop_per_step": FLOP_PER_STEP},
             "clocks": clocks,
         }
         if args.phase_table:
