@@ -148,14 +148,15 @@ enum {  /* task kinds, = TaskKind of the device code */
   OFA_TK_CE_MEAN, OFA_TK_LN_BWD, OFA_TK_LN_DG, OFA_TK_EMB_WTE, OFA_TK_EMB_WPE, OFA_TK_ADAMW, OFA_TK_BARRIER
 };
 enum { OFA_GEMM_NN = 0, OFA_GEMM_NT = 1, OFA_GEMM_TN = 2 };
-enum { OFA_EPI_STORE = 0, OFA_EPI_RES = 1, OFA_EPI_GELU = 2, OFA_EPI_DGELU = 3, OFA_EPI_F32 = 4 };
+enum { OFA_EPI_STORE = 0, OFA_EPI_RES = 1, OFA_EPI_GELU = 2, OFA_EPI_DGELU = 3, OFA_EPI_F32 = 4,
+       OFA_EPI_DR = 5 /* C = acc and p[4][b,h,t] = sum over head h's columns of C * aux: attention backward's row term fused into the GEMM that produces dO */ };
 
 /* One phase = ntasks independent block-sized tasks (PhaseDesc, ofa.cu:89-95). Pointers are DEVICE pointers obtained
  * from ofa_dev_alloc. For GEMM phases ntasks/tiles are derived from M,N,K and the TMA descriptors are built here. */
 typedef struct {
   int kind, layout, epi, accumulate;
   int M, N, K, lda, ldb, ldc, ldaux, nsub;
-  void* p[10];              /* GEMM: p[0]=A p[1]=B p[2]=C p[3]=aux; other kinds: the argument order of the device task */
+  void* p[10];              /* GEMM: p[0]=A p[1]=B p[2]=C p[3]=aux (p[4] = row-term output for OFA_EPI_DR); other kinds: the argument order of the device task */
   size_t n;
   int i0, i1, i2;
 } ofa_phase;

@@ -99,8 +99,9 @@ __device__ __forceinline__ void block_exit(GemmPipe& gp, unsigned char* smem, De
 }
 
 // ---------------------------------------------------------------------------------------------- epilogue math
+// Returns, for GE_DR, the dot product of the eight stored (bf16-rounded) values with the eight aux values; 0 otherwise.
 template <int EPI>
-__device__ __forceinline__ void epi_store8(const GemmArgs& g, size_t row, int col, const float* acc, uint4 auxv) {
+__device__ __forceinline__ float epi_store8(const GemmArgs& g, size_t row, int col, const float* acc, uint4 auxv) {
   if constexpr (EPI == GE_F32) {
     float* dst = reinterpret_cast<float*>(g.C) + row * g.ldc + col;
     float4 v0 = make_float4(acc[0], acc[1], acc[2], acc[3]), v1 = make_float4(acc[4], acc[5], acc[6], acc[7]);
@@ -109,6 +110,7 @@ __device__ __forceinline__ void epi_store8(const GemmArgs& g, size_t row, int co
       v0.x += o0.x; v0.y += o0.y; v0.z += o0.z; v0.w += o0.w; v1.x += o1.x; v1.y += o1.y; v1.z += o1.z; v1.w += o1.w;
     }
     *reinterpret_cast<float4*>(dst) = v0; *reinterpret_cast<float4*>(dst + 4) = v1;
+    return 0.f;
   } else {
     float v[8];
 #pragma unroll
@@ -130,7 +132,16 @@ __device__ __forceinline__ void epi_store8(const GemmArgs& g, size_t row, int co
 #pragma unroll
       for (int i = 0; i < 8; i++) v[i] *= gelu_bwd<true>(p[i]);
     }
-    *reinterpret_cast<uint4*>(C + row * g.ldc + col) = pack8(v);
+    const uint4 out = pack8(v);
+    *reinterpret_cast<uint4*>(C + row * g.ldc + col) = out;
+    if constexpr (EPI == GE_DR) {
+      float c[8], o[8]; unpack8(out, c); unpack8(auxv, o);
+      float s = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; i++) s = fmaf(c[i], o[i], s);
+      return s;
+    }
+    return 0.f;
   }
 }
 
@@ -141,7 +152,7 @@ __device__ __forceinline__ void gemm_tc_task(const GemmArgs& g, int tiles_m, int
                                              DevStatus* st, int phase_id) {
   using CF = Cfg<BN>;
   constexpr bool A_MN = (LAYOUT == GL_TN), B_MN = (LAYOUT != GL_NT);
-  constexpr bool HAS_AUX_IN = (EPI == GE_RES || EPI == GE_DGELU);
+  constexpr bool HAS_AUX_IN = (EPI == GE_RES || EPI == GE_DGELU || EPI == GE_DR);
   constexpr uint32_t IDESC = umma_idesc(A_MN, B_MN, BM, BN);
   constexpr int STAGES = CF::STAGES, W = CF::W;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -239,6 +250,9 @@ __device__ __forceinline__ void gemm_tc_task(const GemmArgs& g, int tiles_m, int
           if (!ok) break;
           tc_fence_after();
         }
+        float drp[EPI == GE_DR ? 8 : 1];                 // GE_DR: this lane's partial row sums, [row slot it][head of the tile]
+#pragma unroll
+        for (int i = 0; i < (EPI == GE_DR ? 8 : 1); i++) drp[i] = 0.f;
 #pragma unroll
         for (int c = 0; c < 4; c++) {
           uint32_t r[32];
@@ -261,9 +275,21 @@ __device__ __forceinline__ void gemm_tc_task(const GemmArgs& g, int tiles_m, int
             const float4 a0 = *reinterpret_cast<const float4*>(stg + rr * 32 + (((2 * cg) ^ (rr & 7)) << 2));
             const float4 a1 = *reinterpret_cast<const float4*>(stg + rr * 32 + (((2 * cg + 1) ^ (rr & 7)) << 2));
             const float acc[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-            epi_store8<EPI>(g, (size_t)(m0 + e * 32 + rr), n0 + half * 128 + c * 32 + cg * 8, acc, auxr[HAS_AUX_IN ? c * 4 + it : 0]);
+            const float part = epi_store8<EPI>(g, (size_t)(m0 + e * 32 + rr), n0 + half * 128 + c * 32 + cg * 8, acc, auxr[HAS_AUX_IN ? c * 4 + it : 0]);
+            if constexpr (EPI == GE_DR) drp[it * 2 + (c >> 1)] += part;
           }
           __syncwarp();
+        }
+        if constexpr (EPI == GE_DR) {                    // a row's 64 columns of a head sit in the 4 lanes of a quad (2 chunks each)
+          // the 128 rows of a tile belong to one sequence (the context length is a multiple of 128): one division per tile
+          const int bseq = m0 / g.dr_T, t0 = m0 - bseq * g.dr_T + e * 32 + (lane >> 2);
+          float* drow = g.dr + ((size_t)bseq * g.dr_H + (n0 + half * 128) / 64) * g.dr_T + t0;
+#pragma unroll
+          for (int i = 0; i < 8; i++) {
+            float v = drp[i];
+            v += __shfl_xor_sync(0xffffffffu, v, 1); v += __shfl_xor_sync(0xffffffffu, v, 2);
+            if (cg == 0) drow[(size_t)(i & 1) * g.dr_T + (i >> 1) * 8] = v;
+          }
         }
       }
     }
@@ -287,6 +313,7 @@ __device__ __noinline__ void run(const PhaseDesc& d, int task, unsigned char* sm
     case GL_NN * 8 + GE_F32:   dispatch_bn<GL_NN, GE_F32>(d, task, smem, gp, st, phase_id); break;      // split-K partial products
     case GL_NT * 8 + GE_STORE: dispatch_bn<GL_NT, GE_STORE>(d, task, smem, gp, st, phase_id); break;
     case GL_NT * 8 + GE_DGELU: dispatch_bn<GL_NT, GE_DGELU>(d, task, smem, gp, st, phase_id); break;
+    case GL_NT * 8 + GE_DR:    gemm_tc_task<GL_NT, GE_DR, 128>(d.g, d.tiles_m, task, smem, gp, st, phase_id); break;
     case GL_TN * 8 + GE_F32:   dispatch_bn<GL_TN, GE_F32>(d, task, smem, gp, st, phase_id); break;
     case GL_TN * 8 + GE_STORE: dispatch_bn<GL_TN, GE_STORE>(d, task, smem, gp, st, phase_id); break;
     default: if (threadIdx.x == 0) raise_abort(st, ST_BAD_DESC, phase_id, task, d.layout * 8 + d.epi); __syncthreads(); break;

@@ -120,13 +120,13 @@ bool prepare_gemm_bf16(PhaseDesc& d, Arena& ar, int nsub_cfg, int nblocks, std::
     err = "GEMM needs M,N % 128 == 0, K % 64 == 0, leading dimensions % 8 == 0 and 16-byte aligned pointers";
     return false;
   }
-  if ((d.epi == GE_RES || d.epi == GE_GELU || d.epi == GE_DGELU) && !g.aux) { err = "GEMM epilogue needs aux"; return false; }
+  if ((d.epi == GE_RES || d.epi == GE_GELU || d.epi == GE_DGELU || d.epi == GE_DR) && !g.aux) { err = "GEMM epilogue needs aux"; return false; }
   // nsub_cfg: n = strips of n tiles (0 = automatic); 2000 + n = the same with 256-wide tiles where N allows. 256-wide tiles are
   // opt-in: with two 48 KB stages per block they measured slower than three 32 KB stages of the 128-wide tile on every model
   // shape except lm_head dW (960 vs 702 TFLOP/s), i.e. the main loop is bound by bytes in flight, not by operand traffic alone.
   const bool want256 = nsub_cfg >= 2000;
   if (want256) nsub_cfg -= 2000;
-  g.bn = (want256 && g.N % 256 == 0) ? 256 : 128;
+  g.bn = (want256 && g.N % 256 == 0 && d.epi != GE_DR) ? 256 : 128;
   const int tm = g.M / 128, tn = g.N / g.bn;
   int nsub = nsub_cfg;
   if (nsub <= 0) {
@@ -488,12 +488,18 @@ bool build_train_graph(ofa_ctx* c) {
       { PhaseDesc d = mk(TK_LN_BWD, rows16); d.p[0] = dh[l]; d.p[1] = dgp2[l]; d.p[2] = dln2[l]; d.p[3] = hb[l]; d.p[4] = mean2[l]; d.p[5] = rstd2[l]; d.p[6] = Wact + lay.g2[l]; d.p[7] = dxs[l + 1];
         addp(s + "ln2 bwd", d, {s + "dln2"}, {}); }
       addp(s + "dgamma2", mkdg(dgp2[l], lay.g2[l]), {s + "ln2 bwd"}, {});
-      addp(s + "dO", mkgemm(GL_NT, GE_STORE, dh[l], D, Wact + lay.wo[l], D, dob[l], D, nullptr, 0, N, D, D, 0), {s + "ln2 bwd"}, {});
+      if (bf) {   // the epilogue also forms the row term of attention backward, D[b,h,t] = sum_d dO * O: no separate pass over dO and O
+        PhaseDesc d = mkgemm(GL_NT, GE_DR, dh[l], D, Wact + lay.wo[l], D, dob[l], D, att[l], D, N, D, D, 0);
+        d.g.dr = Dr[l]; d.g.dr_T = m.T; d.g.dr_H = m.H;
+        addp(s + "dO", d, {s + "ln2 bwd"}, {});
+      } else {
+        addp(s + "dO", mkgemm(GL_NT, GE_STORE, dh[l], D, Wact + lay.wo[l], D, dob[l], D, nullptr, 0, N, D, D, 0), {s + "ln2 bwd"}, {});
+      }
       addp(s + "dWo", mkgemm(GL_TN, wepi, att[l], D, dh[l], D, G(lay.wo[l]), D, nullptr, 0, D, D, N, 0), {s + "ln2 bwd"}, {});
-      { PhaseDesc d = mk(TK_ATT_PREP, bf ? attn_fwd_tasks : 1); d.p[0] = att[l]; d.p[1] = dob[l]; d.p[2] = Dr[l]; addp(s + "attn prep", d, {s + "dO"}, {}); }
+      if (!bf) { PhaseDesc d = mk(TK_ATT_PREP, 1); d.p[0] = att[l]; d.p[1] = dob[l]; d.p[2] = Dr[l]; addp(s + "attn prep", d, {s + "dO"}, {}); }
       { PhaseDesc d = mk(TK_ATT_BWD, attn_bwd_tasks); d.p[0] = qkv[l]; d.p[1] = dob[l]; d.p[2] = lse[l]; d.p[3] = Dr[l]; d.p[4] = dqkv[l]; d.p[5] = att[l];
         if (bf && !cfg.attn_legacy) { std::string e; d.p[6] = const_cast<void*>(make_attn_maps(c->ar, qkv[l], dob[l], N, D, e)); if (!d.p[6]) { ok = false; err = e; } }
-        addp(s + "attn bwd", d, {s + "attn prep"}, {}); }
+        addp(s + "attn bwd", d, {bf ? s + "dO" : s + "attn prep"}, {}); }
       addp(s + "dln1", mkgemm(GL_NT, GE_STORE, dqkv[l], 3 * D, Wact + lay.wqkv[l], 3 * D, dln1[l], D, nullptr, 0, N, D, 3 * D, 0), {s + "attn bwd"}, {});
       addp(s + "dWqkv", mkgemm(GL_TN, wepi, ln1[l], D, dqkv[l], 3 * D, G(lay.wqkv[l]), 3 * D, nullptr, 0, D, 3 * D, N, 0), {s + "attn bwd"}, {});
       { PhaseDesc d = mk(TK_LN_BWD, rows16); d.p[0] = dxs[l]; d.p[1] = dgp1[l]; d.p[2] = dln1[l]; d.p[3] = xs[l]; d.p[4] = mean1[l]; d.p[5] = rstd1[l]; d.p[6] = Wact + lay.g1[l]; d.p[7] = dh[l];
@@ -1080,6 +1086,10 @@ extern "C" int ofa_run_phases(int dtype, const ofa_dims* dims, const ofa_phase* 
       case TK_GEMM:
         d.g.A = s.p[0]; d.g.B = s.p[1]; d.g.C = s.p[2]; d.g.aux = s.p[3]; d.g.M = s.M; d.g.N = s.N; d.g.K = s.K; d.g.lda = s.lda; d.g.ldb = s.ldb; d.g.ldc = s.ldc; d.g.ldaux = s.ldaux;
         d.g.accumulate = s.accumulate;
+        if (s.epi == GE_DR) {   // p[4] = row-term output [B, H, T]; needs the tensor-core path, heads of 64 columns and whole rows of heads in C
+          if (!bf || !s.p[4] || s.layout != GL_NT || s.N != m.D || s.M != m.N) { ar.free_all(); return fail(nullptr, OFA_BAD_ARGUMENT, "row-term epilogue: bf16, NT layout, C = [tokens, d_model], p[4] = output"); }
+          d.g.dr = reinterpret_cast<float*>(s.p[4]); d.g.dr_T = m.T; d.g.dr_H = m.H;
+        }
         if (bf) { if (!prepare_gemm_bf16(d, ar, s.nsub, nblocks, err)) { ar.free_all(); return fail(nullptr, OFA_BAD_ARGUMENT, err); } }
         else prepare_gemm_f32(d);
         break;

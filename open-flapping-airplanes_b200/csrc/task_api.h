@@ -47,6 +47,8 @@ enum GemmEpi : int {
   GE_GELU,        // aux = act(acc); C = act(gelu(aux)) (pre-activation saved for backward)
   GE_DGELU,       // C = act(acc * gelu'(aux))
   GE_F32,         // C(fp32) = acc, or C += acc when `accumulate`
+  GE_DR,          // C = act(acc); dr[b, h, t] = sum over head h's 64 columns of float(C) * aux   (attention backward's row term,
+                  // with C = dO and aux = O; tensor-core path only)
 };
 
 struct GemmArgs {
@@ -58,6 +60,7 @@ struct GemmArgs {
   int bn;                     // tile width of the tensor-core path: 256 when N is a multiple of 256, else 128
   const void* tmA;            // device pointers to the two TMA descriptors (tensor-core path), 64-byte aligned
   const void* tmB;
+  float* dr; int dr_T, dr_H;  // GE_DR only: output [B, H, T] and its dimensions (row = b * T + t, head = column / 64)
 };
 
 struct alignas(16) PhaseDesc {

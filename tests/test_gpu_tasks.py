@@ -218,6 +218,27 @@ def test_gemm_fp32_simt(ofa, K, oracle, layout, epi, M, N, Kd):
         assert relmax(dAux.download(), aux_ref) <= 2e-5
 
 
+def test_gemm_row_term_epilogue(ofa, K, oracle):
+    """dO = dh . Wo^T with the epilogue that also forms attention backward's row term D[b,h,t] = sum_d dO * O (reference: the
+    separate pass of llm/attention/attention.cuh over dO and O, here TK_ATT_PREP)."""
+    Bb, T, H, dh = 2, 256, 12, 64
+    D = H * dh
+    dims = dict(DIMS_S, ctx_len=T, batch=Bb)
+    N = Bb * T
+    g = torch.Generator().manual_seed(11)
+    dhid = rnd(torch.randn(N, D, generator=g) * 0.5, True); Wo = rnd(torch.randn(D, D, generator=g) * 0.05, True); O = rnd(torch.randn(N, D, generator=g), True)
+    d_dh = ofa.DeviceBuffer.from_host(dhid.numpy(), "bf16"); d_W = ofa.DeviceBuffer.from_host(Wo.numpy(), "bf16"); d_O = ofa.DeviceBuffer.from_host(O.numpy(), "bf16")
+    d_dO = ofa.DeviceBuffer((N, D), "bf16"); d_Dr = ofa.DeviceBuffer((Bb, H, T), np.float32); d_Dr2 = ofa.DeviceBuffer((Bb, H, T), np.float32)
+    ph = ofa.gemm_phase(1, K.EPI_DR, N, D, D, d_dh, D, d_W, D, d_dO, D, d_O, D)
+    ph.p[4] = d_Dr.ptr
+    ofa.run_phases(K.DTYPE_BF16, dims, [ph, ofa.phase(K.TK_ATT_PREP, [d_O, d_dO, d_Dr2])])
+    dO = d_dO.download()
+    assert relmax(dO, (dhid @ Wo.T).numpy()) <= 2e-2
+    ref = (torch.from_numpy(dO.astype(np.float32)) * O).reshape(Bb, T, H, dh).sum(-1).permute(0, 2, 1).numpy()
+    assert np.abs(d_Dr.download() - ref).max() <= 1e-3 * max(1.0, np.abs(ref).max())
+    assert np.abs(d_Dr.download() - d_Dr2.download()).max() <= 1e-3 * max(1.0, np.abs(ref).max())
+
+
 @pytest.mark.parametrize("legacy", [0, 1])            # 0: tcgen05 tasks (tensor-memory accumulators), 1: mma.sync tasks
 @pytest.mark.parametrize("B,T", [(2, 256), (1, 1024), (3, 128)])
 def test_attention_bf16_forward_backward(ofa, K, oracle, B, T, legacy):
