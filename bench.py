@@ -153,6 +153,7 @@ def main():
     ap.add_argument("--workload", default="split", choices=["split", "train_only"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--phase-table", action="store_true", help="also print the per-phase busy table to stderr")
+    ap.add_argument("--cfg", action="append", default=[], metavar="FIELD=INT", help="override an integer field of ofa_config (experiments, e.g. gemm_nsub=2, attn_legacy=1); the run is then not the headline configuration")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1")); local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
@@ -190,6 +191,9 @@ def main():
     dp = None
     if world > 1:
         cfg.dp_world, cfg.grad_bf16, cfg.ext_sync = world, 1, 1
+    for kv in args.cfg:
+        k, v = kv.split("=")
+        setattr(cfg, k, int(v))
     mk = ofa.Megakernel(cfg)
     mk.load_weights(init_flat(mk))
     ntok = 1 << 22
@@ -259,7 +263,7 @@ def main():
             "config": {"workload": ("gpt_s V=50304 untied D=768 L=12 H=12 T=1024 B=4 (4096 tok/step/GPU), " +
                                     ("116 train / 24 serve / 8 reserved SMs with concurrent batch-1 greedy decode (6-token prompt, 256 generated, repeating)" if split else "training only on all SMs")),
                        "parallelism": f"dp{world}", "l2": "working set per step (>2 GB) exceeds the 126 MB L2; no flush needed",
-                       "projected_4000_steps_s": ms / K * 4000 / 1e3},
+                       "projected_4000_steps_s": ms / K * 4000 / 1e3, **({"overrides": args.cfg} if args.cfg else {})},
             "decode_tok_s": dec_tok_s, "final_loss": float(losses[-1]), "first_loss": float(losses[0]),
             "e2e": {"value": world * TOKENS_PER_STEP * K / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": int(window.nbytes / K + starts.nbytes / K), "d2h_bytes_per_step": 4},
             "gpu_launches": 1,

@@ -113,9 +113,12 @@ def load():
     global _lib
     if _lib is not None:
         return _lib
-    if not os.path.exists(_build.LIB) or _build.needs_build():
-        _build.build()
-    lib = C.CDLL(_build.LIB)
+    path = os.environ.get("OFA_B200_LIB")        # a prebuilt library elsewhere (a host application's own build, an A/B variant)
+    if not path:
+        if not os.path.exists(_build.LIB) or _build.needs_build():
+            _build.build()
+        path = _build.LIB
+    lib = C.CDLL(path)
     for name, (res, args) in PROTOTYPES.items():
         fn = getattr(lib, name)      # AttributeError = the library does not export what the header declares
         fn.restype = res

@@ -319,8 +319,6 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
         __syncthreads();
         break;
       }
-    } else {
-      __syncthreads();                               // s_sel may be rewritten by thread 0 only after everyone has read it
     }
     u64 t0 = 0;
     if (tid == 0) { t0 = gtimer(); t_sync += t0 - tl1; if (job_id == 1 && C.dp.trace && local == 0 && (ph == 0 || ph == 2)) C.dp.trace[16 + ph] = t0; }
