@@ -445,7 +445,58 @@ bool build_train_graph(ofa_ctx* c) {
       if (l == L - 1) { nd.push_back(Span{lay.gf, D}); deps.push_back("lnf dgamma"); }
       addp("adamw L" + std::to_string(l), mkadam(off, end - off, nd), gate("adamw L" + std::to_string(l), deps), {});
     };
-    const bool interleave_adam = train && !ext && cfg.adam_interleave;
+    const bool interleave_adam = train && !ext && cfg.adam_interleave == 1;
+    // cfg.adam_interleave = n >= 2 (off by default: measured 0.9-1.5 % slower per step for n = 6..48, because an AdamW task is bound
+    // by what one block keeps in flight - 88 us beside GEMMs against 100 us beside 231 others like it - so moving it buys little and
+    // costs the chain its earliest blocks): AdamW trickles through the backward pass. As soon as a tensor group's gradient is final its
+    // update is queued, and after every backward phase up to n optimizer tasks are emitted as a small phase of their own. A
+    // backward phase of 192 strips leaves 40 of the 232 training blocks without a ticket; they take these tasks instead of
+    // waiting, and a memory-bound task that runs beside GEMMs instead of beside 231 others like it finishes several times
+    // sooner. The group's usual phase name goes to a 1-task phase behind its last chunk that waits for all of them, so the next
+    // step's forward pass still has one thing to wait for.
+    struct AdamItem { std::string name; size_t off, n; std::vector<Span> nd; std::vector<std::string> deps, parts; int next_task = 0, chunks = 0; };
+    std::vector<AdamItem> adam_q; size_t adam_q_head = 0;
+    const int trickle_n = (train && !ext && cfg.adam_interleave >= 2) ? cfg.adam_interleave : 0;
+    bool in_trickle = false;
+    auto mkadam_range = [&](size_t off, size_t n, const std::vector<Span>& nodecay_abs) {
+      std::vector<Span> clipped;
+      for (const Span& sp : nodecay_abs) {
+        const size_t lo = std::max(sp.off, off), hi = std::min(sp.off + sp.n, off + n);
+        if (lo < hi) clipped.push_back(Span{lo, hi - lo});
+      }
+      return mkadam(off, n, clipped);
+    };
+    auto trickle = [&](bool flush) {
+      if (!trickle_n || in_trickle) return;
+      in_trickle = true;
+      long budget = flush ? (1L << 40) : trickle_n;
+      while (budget > 0 && adam_q_head < adam_q.size()) {
+        AdamItem& it = adam_q[adam_q_head];
+        const int total = (int)((it.n + ew::OPT_CHUNK - 1) / ew::OPT_CHUNK);
+        int cnt = (int)std::min<long>(budget, total - it.next_task);
+        if (total - it.next_task - cnt < trickle_n / 2) cnt = total - it.next_task;        // no tiny remainder
+        const bool last = it.next_task + cnt == total;
+        const size_t o = it.off + (size_t)it.next_task * ew::OPT_CHUNK, nn = std::min((size_t)cnt * ew::OPT_CHUNK, it.off + it.n - o);
+        if (last && it.chunks == 0) {                    // the whole group in one piece: an ordinary optimizer phase
+          addp(it.name, mkadam_range(o, nn, it.nd), it.deps, {});
+        } else {
+          // chunks are independent of one another (a chain would serialise the group and park the blocks that hold the
+          // later chunks' tickets); one 1-task phase in front says "the gradient is final", one behind says "all chunks done"
+          if (it.chunks == 0) addp(it.name + " ready", mk(TK_BARRIER, 1), it.deps, {});
+          const std::string nm = it.name + " ." + std::to_string(it.chunks);
+          addp(nm, mkadam_range(o, nn, it.nd), {it.name + " ready"}, {});
+          it.parts.push_back(nm);
+          if (last) addp(it.name, mk(TK_BARRIER, 1), it.parts, {});
+        }
+        it.chunks++; it.next_task += cnt; budget -= cnt;
+        if (last) adam_q_head++;
+      }
+      in_trickle = false;
+    };
+    auto addb = [&](const std::string& name, const PhaseDesc& d, std::vector<std::string> deps0, std::vector<std::string> deps_prev) {
+      addp(name, d, deps0, deps_prev);
+      trickle(false);
+    };
 
     // ---- backward
     {
@@ -470,42 +521,50 @@ bool build_train_graph(ofa_ctx* c) {
         addp("head dX", dsum, parts, {});
       }
     }
-    addp("head dW", mkgemm(GL_TN, wepi, logits, V, lnf, D, G(lay.head), D, nullptr, 0, V, D, N, 0), {"cross-entropy"}, {});
+    addb("head dW", mkgemm(GL_TN, wepi, logits, V, lnf, D, G(lay.head), D, nullptr, 0, V, D, N, 0), {"cross-entropy"}, {});
+    if (trickle_n && !lay.tied) { AdamItem it; it.name = "adamw head"; it.off = lay.head; it.n = V * D; it.deps = {"head dW", "head dX"}; adam_q.push_back(it); }
     if (ext && !lay.tied) signal(0);
     { PhaseDesc d = mk(TK_LN_BWD, rows16); d.p[0] = dxs[L]; d.p[1] = dgpf; d.p[2] = dxf; d.p[3] = xs[L]; d.p[4] = meanf; d.p[5] = rstdf; d.p[6] = Wact + lay.gf; d.p[7] = nullptr;
-      addp("lnf bwd", d, {"head dX"}, {}); }
+      addb("lnf bwd", d, {"head dX"}, {}); }
     auto mkdg = [&](float* part, size_t goff) { PhaseDesc d = mk(TK_LN_DG, (int)((D + NTHR - 1) / NTHR)); d.p[0] = G(goff); d.p[1] = part; d.i0 = 0; d.i1 = gbf ? 1 : 0; return d; };
-    addp("lnf dgamma", mkdg(dgpf, lay.gf), {"lnf bwd"}, {});
+    addb("lnf dgamma", mkdg(dgpf, lay.gf), {"lnf bwd"}, {});
     std::string g = "lnf bwd";
     const int attn_bwd_tasks = bf ? 2 * attn_fwd_tasks : m.B * m.H;
     for (int l = L - 1; l >= 0; l--) {
       const std::string s = "L" + std::to_string(l) + " ";
-      addp(s + "dpre", mkgemm(GL_NT, GE_DGELU, dxs[l + 1], D, Wact + lay.wdn[l], D, dpre[l], FF, upre[l], FF, N, FF, D, 0), {g}, {});
-      addp(s + "dWdown", mkgemm(GL_TN, wepi, uact[l], FF, dxs[l + 1], D, G(lay.wdn[l]), D, nullptr, 0, FF, D, N, 0), {g}, {});
+      addb(s + "dpre", mkgemm(GL_NT, GE_DGELU, dxs[l + 1], D, Wact + lay.wdn[l], D, dpre[l], FF, upre[l], FF, N, FF, D, 0), {g}, {});
+      addb(s + "dWdown", mkgemm(GL_TN, wepi, uact[l], FF, dxs[l + 1], D, G(lay.wdn[l]), D, nullptr, 0, FF, D, N, 0), {g}, {});
       if (interleave_adam) { if (l == L - 1) { if (!lay.tied) emit_adam_head(); } else emit_adam_layer(l + 1); }
-      addp(s + "dln2", mkgemm(GL_NT, GE_STORE, dpre[l], FF, Wact + lay.wup[l], FF, dln2[l], D, nullptr, 0, N, D, FF, 0), {s + "dpre"}, {});
-      addp(s + "dWup", mkgemm(GL_TN, wepi, ln2[l], D, dpre[l], FF, G(lay.wup[l]), FF, nullptr, 0, D, FF, N, 0), {s + "dpre"}, {});
+      addb(s + "dln2", mkgemm(GL_NT, GE_STORE, dpre[l], FF, Wact + lay.wup[l], FF, dln2[l], D, nullptr, 0, N, D, FF, 0), {s + "dpre"}, {});
+      addb(s + "dWup", mkgemm(GL_TN, wepi, ln2[l], D, dpre[l], FF, G(lay.wup[l]), FF, nullptr, 0, D, FF, N, 0), {s + "dpre"}, {});
       { PhaseDesc d = mk(TK_LN_BWD, rows16); d.p[0] = dh[l]; d.p[1] = dgp2[l]; d.p[2] = dln2[l]; d.p[3] = hb[l]; d.p[4] = mean2[l]; d.p[5] = rstd2[l]; d.p[6] = Wact + lay.g2[l]; d.p[7] = dxs[l + 1];
-        addp(s + "ln2 bwd", d, {s + "dln2"}, {}); }
-      addp(s + "dgamma2", mkdg(dgp2[l], lay.g2[l]), {s + "ln2 bwd"}, {});
+        addb(s + "ln2 bwd", d, {s + "dln2"}, {}); }
+      addb(s + "dgamma2", mkdg(dgp2[l], lay.g2[l]), {s + "ln2 bwd"}, {});
       if (bf) {   // the epilogue also forms the row term of attention backward, D[b,h,t] = sum_d dO * O: no separate pass over dO and O
         PhaseDesc d = mkgemm(GL_NT, GE_DR, dh[l], D, Wact + lay.wo[l], D, dob[l], D, att[l], D, N, D, D, 0);
         d.g.dr = Dr[l]; d.g.dr_T = m.T; d.g.dr_H = m.H;
-        addp(s + "dO", d, {s + "ln2 bwd"}, {});
+        addb(s + "dO", d, {s + "ln2 bwd"}, {});
       } else {
-        addp(s + "dO", mkgemm(GL_NT, GE_STORE, dh[l], D, Wact + lay.wo[l], D, dob[l], D, nullptr, 0, N, D, D, 0), {s + "ln2 bwd"}, {});
+        addb(s + "dO", mkgemm(GL_NT, GE_STORE, dh[l], D, Wact + lay.wo[l], D, dob[l], D, nullptr, 0, N, D, D, 0), {s + "ln2 bwd"}, {});
       }
-      addp(s + "dWo", mkgemm(GL_TN, wepi, att[l], D, dh[l], D, G(lay.wo[l]), D, nullptr, 0, D, D, N, 0), {s + "ln2 bwd"}, {});
-      if (!bf) { PhaseDesc d = mk(TK_ATT_PREP, 1); d.p[0] = att[l]; d.p[1] = dob[l]; d.p[2] = Dr[l]; addp(s + "attn prep", d, {s + "dO"}, {}); }
+      addb(s + "dWo", mkgemm(GL_TN, wepi, att[l], D, dh[l], D, G(lay.wo[l]), D, nullptr, 0, D, D, N, 0), {s + "ln2 bwd"}, {});
+      if (!bf) { PhaseDesc d = mk(TK_ATT_PREP, 1); d.p[0] = att[l]; d.p[1] = dob[l]; d.p[2] = Dr[l]; addb(s + "attn prep", d, {s + "dO"}, {}); }
       { PhaseDesc d = mk(TK_ATT_BWD, attn_bwd_tasks); d.p[0] = qkv[l]; d.p[1] = dob[l]; d.p[2] = lse[l]; d.p[3] = Dr[l]; d.p[4] = dqkv[l]; d.p[5] = att[l];
         if (bf && !cfg.attn_legacy) { std::string e; d.p[6] = const_cast<void*>(make_attn_maps(c->ar, qkv[l], dob[l], N, D, e)); if (!d.p[6]) { ok = false; err = e; } }
-        addp(s + "attn bwd", d, {bf ? s + "dO" : s + "attn prep"}, {}); }
-      addp(s + "dln1", mkgemm(GL_NT, GE_STORE, dqkv[l], 3 * D, Wact + lay.wqkv[l], 3 * D, dln1[l], D, nullptr, 0, N, D, 3 * D, 0), {s + "attn bwd"}, {});
-      addp(s + "dWqkv", mkgemm(GL_TN, wepi, ln1[l], D, dqkv[l], 3 * D, G(lay.wqkv[l]), 3 * D, nullptr, 0, D, 3 * D, N, 0), {s + "attn bwd"}, {});
+        addb(s + "attn bwd", d, {bf ? s + "dO" : s + "attn prep"}, {}); }
+      addb(s + "dln1", mkgemm(GL_NT, GE_STORE, dqkv[l], 3 * D, Wact + lay.wqkv[l], 3 * D, dln1[l], D, nullptr, 0, N, D, 3 * D, 0), {s + "attn bwd"}, {});
+      addb(s + "dWqkv", mkgemm(GL_TN, wepi, ln1[l], D, dqkv[l], 3 * D, G(lay.wqkv[l]), 3 * D, nullptr, 0, D, 3 * D, N, 0), {s + "attn bwd"}, {});
       { PhaseDesc d = mk(TK_LN_BWD, rows16); d.p[0] = dxs[l]; d.p[1] = dgp1[l]; d.p[2] = dln1[l]; d.p[3] = xs[l]; d.p[4] = mean1[l]; d.p[5] = rstd1[l]; d.p[6] = Wact + lay.g1[l]; d.p[7] = dh[l];
-        addp(s + "ln1 bwd", d, {s + "dln1"}, {}); }
-      addp(s + "dgamma1", mkdg(dgp1[l], lay.g1[l]), {s + "ln1 bwd"}, {});
+        addb(s + "ln1 bwd", d, {s + "dln1"}, {}); }
+      addb(s + "dgamma1", mkdg(dgp1[l], lay.g1[l]), {s + "ln1 bwd"}, {});
       g = s + "ln1 bwd";
+      if (trickle_n) {
+        AdamItem it; it.name = "adamw L" + std::to_string(l); it.off = lay.g1[l]; it.n = ((l + 1 < L) ? lay.g1[l + 1] : lay.gf + D) - lay.g1[l];
+        it.nd = {Span{lay.g1[l], D}, Span{lay.g2[l], D}};
+        it.deps = {s + "dWdown", s + "dWup", s + "dgamma2", s + "dWo", s + "dWqkv", s + "dgamma1", s + "ln1 bwd"};
+        if (l == L - 1) { it.nd.push_back(Span{lay.gf, D}); it.deps.push_back("lnf dgamma"); }
+        adam_q.push_back(it);
+      }
       if (ext) {
         Bucket& b = buckets[bucket_of_layer[l]];
         for (const char* nm : {"dWdown", "dWup", "dgamma2", "dWo", "dWqkv", "dgamma1", "ln1 bwd"}) b.producers.push_back(s + nm);
@@ -526,6 +585,7 @@ bool build_train_graph(ofa_ctx* c) {
         PhaseDesc d = mk(TK_EXT_WAIT, 1); d.p[0] = c->d_ext_done + bi;
         addp("allreduce done " + std::to_string(bi), d, {"grads ready " + std::to_string(bi)}, {});
       }
+      trickle(true);                                   // what the backward pass had no room for
       if (!lay.tied && !id.count("adamw head")) emit_adam_head();
       for (int l = L - 1; l >= 0; l--) if (!id.count("adamw L" + std::to_string(l))) emit_adam_layer(l);
       if (!lay.tied) end_deps.push_back("adamw head");
