@@ -2,7 +2,7 @@
 constants set to small configurations, and running its GPT class, init recipe, LR schedule, batch sampler and AdamW
 parameter groups on the CPU. Run once in the build container (the reference checkout is not available elsewhere):
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path to a checkout of the reference>
 
 The fixtures pin oracle/gpt_oracle.py (tests/test_oracle_golden.py). Stored: the initial weights' checksums and samples,
 step-0 loss, every gradient tensor of step 0, weights after one and three AdamW steps (sampled), the loss of the first
@@ -79,7 +79,9 @@ def run_config(c, name, V, D, L, H, T, B, nsteps, ntok, constant_lr=None):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <path to a checkout of the reference>")
+    ref_root = sys.argv[1]
     torch.set_num_threads(4)
     c = load_common(ref_root)
     # schedule probes at the reference's own constants
