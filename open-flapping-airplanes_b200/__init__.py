@@ -6,6 +6,7 @@ The directory name contains a hyphen, so import it with importlib.import_module(
 from . import build as build_mod
 from . import capi
 from . import dp
+from . import files
 from .host import Megakernel, OfaError, default_config, flat_from_named, PARAM_ORDER_DOC
 from .tasks import DeviceBuffer, run_phases, gemm_phase, phase, bf16_round, to_bf16_bits, from_bf16_bits
 

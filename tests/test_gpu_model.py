@@ -183,3 +183,29 @@ def test_gpt_s_full_size_properties(ofa, oracle):
     w = mk.read_weights()
     assert np.all(np.isfinite(w)) and not np.array_equal(w, flat)
     mk.close()
+
+
+def test_checkpoint_resume_continues_bit_for_bit(ofa, oracle, tmp_path):
+    """4 steps in one context == 2 steps, checkpoint to files, a fresh context loaded from them, 2 more steps: same losses, weights and
+    optimizer state to the bit (the reference has no resume; its --dump-w file is the weights file of the checkpoint)."""
+    ocfg, w0, tokens, starts, a = tiny_setup(ofa, oracle, nsteps=4)
+    a.run(4)
+    la, wa = a.losses().copy(), a.read_weights(); ma, va = a.read_adam()
+    a.close()
+    ocfg, w0, tokens, starts, b = tiny_setup(ofa, oracle, nsteps=4)
+    b.run(2)
+    lb = b.losses().copy()
+    meta = ofa.files.save_checkpoint(b, tmp_path / "ckpt")
+    assert meta["steps_done"] == 2 and (tmp_path / "ckpt" / "weights.f32").stat().st_size == 4 * b.num_params
+    b.close()
+    ocfg, w0, tokens, starts, c = tiny_setup(ofa, oracle, nsteps=4)
+    ofa.files.load_checkpoint(c, tmp_path / "ckpt")
+    assert c.steps_done == 2
+    c.run(2)
+    np.testing.assert_array_equal(np.concatenate([lb[:2], c.losses()[-2:]]), la)
+    np.testing.assert_array_equal(c.read_weights(), wa)
+    mc, vc = c.read_adam()
+    np.testing.assert_array_equal(mc, ma); np.testing.assert_array_equal(vc, va)
+    ofa.files.write_loss_log(tmp_path / "loss.txt", la)
+    assert (tmp_path / "loss.txt").read_text().splitlines()[0] == "0 %.6f" % la[0]
+    c.close()
