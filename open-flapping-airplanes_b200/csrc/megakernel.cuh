@@ -287,6 +287,8 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
       }
       s_sel[0] = res; s_sel[1] = step; s_sel[2] = ph; s_sel[3] = local;
       tl1 = gtimer(); t_claim += (tl1 - tl0) - (waited - w_before);
+    } else if (tid < 16) {
+      sched_cp_wait();                               // the descriptor requested at the end of the last task: visible to all after the barrier below
     }
     __syncthreads();
     int res = s_sel[0];
@@ -296,12 +298,13 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
     // longer holds it, and the chain of dependent global loads that decoding it would take was a measurable part of the
     // per-task overhead. Two slots: the next phase's descriptor is requested at the end of a task (below), so a block that
     // moves on by one phase - the common case when phases have about as many tasks as there are blocks - finds it here.
-    if (tid < 16) sched_cp_wait();
     if (ph != cached_ph) {
-      if (ph == ahead_ph) { slot ^= 1; ahead_ph = cached_ph; }
-      else if (tid < (int)(sizeof(PhaseDesc) / 4)) reinterpret_cast<uint32_t*>(ctrl + 256 + 256 * slot)[tid] = __ldg(reinterpret_cast<const uint32_t*>(J.ph + ph) + tid);
-      cached_ph = ph;
-      __syncthreads();
+      if (ph == ahead_ph) { slot ^= 1; ahead_ph = cached_ph; cached_ph = ph; }      // already there: no second barrier (-0.9 % per step)
+      else {
+        if (tid < (int)(sizeof(PhaseDesc) / 4)) reinterpret_cast<uint32_t*>(ctrl + 256 + 256 * slot)[tid] = __ldg(reinterpret_cast<const uint32_t*>(J.ph + ph) + tid);
+        cached_ph = ph;
+        __syncthreads();
+      }
     }
     const PhaseDesc& d = *reinterpret_cast<const PhaseDesc*>(ctrl + 256 + 256 * slot);
     bool filled = false;
