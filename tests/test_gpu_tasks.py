@@ -266,6 +266,30 @@ def test_attention_bf16_forward_backward(ofa, K, oracle, B, T, legacy):
     np.testing.assert_array_equal(first, d_dqkv.download())
 
 
+@pytest.mark.parametrize("legacy", [0, 1])
+def test_attention_bf16_forward_with_growing_row_maxima(ofa, K, oracle, legacy):
+    """Keys whose scores grow along the sequence: a row's maximum rises by far more than 2^8 from one key tile to the next, so the
+    tcgen05 forward task has to rescale the output row it keeps in tensor memory (its rare path) again and again."""
+    B, T, H, dh = 2, 512, 12, 64
+    D = H * dh
+    dims = dict(DIMS_S, ctx_len=T, batch=B)
+    N = B * T
+    g = torch.Generator().manual_seed(7)
+    qkv = torch.randn(N, 3 * D, generator=g)
+    ramp = (torch.arange(N) % T).float().unsqueeze(1) / T                  # 0 .. 1 along each sequence
+    qkv[:, :D] = 1.0 + 0.1 * qkv[:, :D]                                   # queries: mostly a positive constant direction
+    qkv[:, D:2 * D] = ramp * 3.0 + 0.1 * qkv[:, D:2 * D]                  # keys: growing along the sequence -> scores up to ~190 * 0.125
+    qkv = rnd(qkv, True)
+    d_qkv = ofa.DeviceBuffer.from_host(qkv.numpy(), "bf16")
+    d_o = ofa.DeviceBuffer((N, D), "bf16"); d_lse = ofa.DeviceBuffer((B, H, T), np.float32)
+    ofa.run_phases(K.DTYPE_BF16, dims, [ofa.phase(K.TK_ATT_FWD, [d_qkv, d_o, d_lse], i0=legacy)])
+    o_ref, lse_ref = oracle.attention_ref(qkv, B, T, H, dh)
+    spread = float(lse_ref.max() - lse_ref.min())
+    assert spread > 12.0                                                   # natural log: far beyond 8 bits between the first and the last tiles
+    assert relmax(d_o.download(), o_ref) <= 2e-2
+    assert np.abs(d_lse.download() - lse_ref.numpy()).max() <= 2e-3 * max(1.0, float(lse_ref.abs().max()))
+
+
 def test_attention_fp32_forward_backward(ofa, K, oracle):
     B, T, H, dh = 4, 64, 4, 16
     D = H * dh
