@@ -286,6 +286,15 @@ def main():
             print("  per category (block-ms per step, share of busy, mean us per task, block-ms per step waiting for its dependencies):", file=sys.stderr)
             for k, (b, n, w) in sorted(cat.items(), key=lambda kv: -kv[1][0]):
                 print(f"    {k:22s} {b / 1e6 / K:8.3f}  {100.0 * b / tot:5.1f} %  {b / 1e3 / K / max(1, n):8.2f} us/task  ({n} tasks)  wait {w / 1e6 / K:8.3f}", file=sys.stderr)
+            win = mk.phase_windows(); names = [p["name"] for p in mk.phases()]
+            valid = [(a, b, n) for (a, b), n in zip(win, names) if a != 0xFFFFFFFFFFFFFFFF and b]
+            if valid:
+                t0 = min(a for a, _, _ in valid)
+                print("  phase windows in the last step (first task start -> last task end, ms from the step's first task):", file=sys.stderr)
+                for a, b, n in valid:
+                    if n.startswith("L") and not (n.startswith("L0 ") or n.startswith("L11 ") or n.startswith("L5 ")):
+                        continue
+                    print(f"    {n:22s} {(a - t0) / 1e6:8.3f} -> {(b - t0) / 1e6:8.3f}  ({(b - a) / 1e3:7.1f} us)", file=sys.stderr)
             for p in sorted(mk.phases(), key=lambda p: -p["busy_ns"])[:40]:
                 print(f"  {p['name']:24s} tasks {p['ntasks']:6d}  busy {p['busy_ns'] / 1e6 / K:8.3f} ms/step  {100.0 * p['busy_ns'] / tot:5.1f} %", file=sys.stderr)
         if world == 1 and not args.no_cpu_baseline:

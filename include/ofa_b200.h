@@ -115,6 +115,8 @@ int ofa_num_phases(const ofa_ctx* ctx);
 int ofa_phase_info(const ofa_ctx* ctx, int phase, char* name, size_t name_cap, int* kind, int* ntasks, unsigned long long* busy_ns);
 /* nanoseconds the training blocks spent waiting for the dependencies of tasks of this phase during the last launch (summed over blocks): shows which phase boundaries the step loses time at; no counterpart in the reference's report */
 int ofa_phase_wait_ns(const ofa_ctx* ctx, int phase, unsigned long long* wait_ns);
+/* %globaltimer ns at which the first task of the phase started and the last one ended, in the LAST step of the last launch (the "phase wall-clock at step" table of the report, ofa.cu:735-743); first = all ones when the phase had no task in that step */
+int ofa_phase_window(const ofa_ctx* ctx, int phase, unsigned long long* first_ns, unsigned long long* last_ns);
 /* busy nanoseconds of every block in the last launch: out[2*block + job] (job 0 training, 1 serving) for the first 2*grid entries (ofa.cu:313 blk_busy), then four rows of grid entries each: time the block's scheduler thread spent waiting for training dependencies, claiming tickets, handing the task to the block, and signalling completion; n <= 6 * grid size */
 int ofa_read_block_busy(ofa_ctx* ctx, unsigned long long* out, size_t n);
 /* in-kernel trace of the serving job (the reference's DTRACE, decode_wide.cuh:11-16): %globaltimer stamps of the stage boundaries inside task 0 of layer 0 (slots 0-4 QKV, 8-12 UP+DOWN, 16-19 scheduler-side start/end of those tasks), last token of the last launch */

@@ -67,6 +67,7 @@ PROTOTYPES = {
     "ofa_read_losses": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t]),
     "ofa_read_step_times": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t]),
     "ofa_num_phases": (C.c_int, [C.c_void_p]),
+    "ofa_phase_window": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_ulonglong), C.POINTER(C.c_ulonglong)]),
     "ofa_phase_wait_ns": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_ulonglong)]),
     "ofa_phase_info": (C.c_int, [C.c_void_p, C.c_int, C.c_char_p, C.c_size_t, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_ulonglong)]),
     "ofa_read_block_busy": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t]),

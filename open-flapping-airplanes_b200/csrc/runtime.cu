@@ -976,6 +976,10 @@ extern "C" int ofa_launch(ofa_ctx* c, int nsteps) {
   cudaMemsetAsync(c->d_blk_busy, 0, sizeof(unsigned long long) * 6 * c->nblocks, c->stream);
   cudaMemsetAsync(c->d_dec_phase_busy, 0, sizeof(unsigned long long) * std::max<size_t>(1, c->dec_ph.size()), c->stream);
   C.smem_bytes = c->smem;
+  // wall-clock window of every phase in the last step of this launch (the reference's "phase wall-clock at step" table, ofa.cu:735-743)
+  C.prof_step = nsteps - 1;
+  cudaMemsetAsync(c->d_phase_first, 0xFF, sizeof(unsigned long long) * std::max<size_t>(1, c->train_ph.size()), c->stream);
+  cudaMemsetAsync(c->d_phase_last, 0, sizeof(unsigned long long) * std::max<size_t>(1, c->train_ph.size()), c->stream);
   const Ctx& L = C;
   cudaEventRecord(c->ev0, c->stream);
   cudaError_t e = c->bf ? launch_kernel<bf16, 768, 64>(L, c->nblocks, c->smem, c->stream) : launch_kernel<float, 64, 16>(L, c->nblocks, c->smem, c->stream);
@@ -1043,6 +1047,14 @@ extern "C" int ofa_phase_info(const ofa_ctx* c, int phase, char* name, size_t na
   if (ntasks) *ntasks = p.d.ntasks;
   if (busy_ns) { if (c->dry) *busy_ns = 0; else { cudaSetDevice(c->device); cudaMemcpy(busy_ns, c->d_phase_busy + phase, 8, cudaMemcpyDeviceToHost); } }
   return OFA_OK;
+}
+extern "C" int ofa_phase_window(const ofa_ctx* c, int phase, unsigned long long* first_ns, unsigned long long* last_ns) {
+  if (!c || !first_ns || !last_ns || phase < 0 || phase >= (int)c->train_ph.size()) return OFA_BAD_ARGUMENT;
+  if (c->dry) { *first_ns = *last_ns = 0; return OFA_OK; }
+  cudaSetDevice(c->device);
+  const bool ok = cudaMemcpy(first_ns, c->d_phase_first + phase, 8, cudaMemcpyDeviceToHost) == cudaSuccess &&
+                  cudaMemcpy(last_ns, c->d_phase_last + phase, 8, cudaMemcpyDeviceToHost) == cudaSuccess;
+  return ok ? OFA_OK : OFA_CUDA_ERROR;
 }
 extern "C" int ofa_phase_wait_ns(const ofa_ctx* c, int phase, unsigned long long* wait_ns) {
   if (!c || !wait_ns || phase < 0 || phase >= (int)c->train_ph.size()) return OFA_BAD_ARGUMENT;

@@ -153,6 +153,15 @@ class Megakernel:
             res.append({"name": name.value.decode(), "kind": kind.value, "ntasks": nt.value, "busy_ns": busy.value, "wait_ns": wait.value})
         return res
 
+    def phase_windows(self):
+        """(first task start, last task end) in %globaltimer ns of every training phase in the last step of the last launch"""
+        res = []
+        for i in range(self.lib.ofa_num_phases(self.h)):
+            a, b = C.c_ulonglong(), C.c_ulonglong()
+            self._chk(self.lib.ofa_phase_window(self.h, i, C.byref(a), C.byref(b)))
+            res.append((a.value, b.value))
+        return res
+
     def block_busy_ns(self, nblocks=296):
         out = np.zeros(2 * nblocks, dtype=np.uint64)
         self._chk(self.lib.ofa_read_block_busy(self.h, out.ctypes.data_as(C.c_void_p), out.size))
