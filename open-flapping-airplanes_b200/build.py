@@ -9,8 +9,9 @@ import subprocess
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(CSRC, "libofa_b200.so")
+CLI = os.path.join(CSRC, "ofa_cli")              # the command-line host (csrc/ofa_cli.cpp), linked against LIB
 SOURCES = ["runtime.cu", "noalloc.cu"]
-HEADERS = ["common.cuh", "task_api.h", "elementwise.cuh", "gemm_tc.cuh", "attn_mma.cuh", "simt_f32.cuh", "decode.cuh",
+HEADERS = ["common.cuh", "task_api.h", "elementwise.cuh", "gemm_tc.cuh", "attn_mma.cuh", "attn_tc.cuh", "simt_f32.cuh", "decode.cuh",
            "megakernel.cuh", os.path.join("..", "..", "include", "ofa_b200.h")]
 
 
@@ -46,3 +47,19 @@ def build(force=False, verbose=False):
 
 if __name__ == "__main__":
     print(build(force=True, verbose=True))
+
+
+def build_cli(force=False):
+    """Compile csrc/ofa_cli.cpp (plain C++ over the C ABI) next to the library. Returns the path of the binary."""
+    src = os.path.join(CSRC, "ofa_cli.cpp")
+    hdr = os.path.join(CSRC, "..", "..", "include", "ofa_b200.h")
+    if not force and os.path.exists(CLI) and os.path.getmtime(CLI) >= max(os.path.getmtime(src), os.path.getmtime(hdr)):
+        return CLI
+    build()
+    cxx = shutil.which("g++") or shutil.which("c++")
+    if not cxx:
+        raise RuntimeError("no C++ compiler for ofa_cli")
+    r = subprocess.run([cxx, "-O2", "-std=c++17", "-o", CLI, src, "-L" + CSRC, "-lofa_b200", "-Wl,-rpath,$ORIGIN"], capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("building ofa_cli failed:\n" + r.stdout + r.stderr)
+    return CLI
