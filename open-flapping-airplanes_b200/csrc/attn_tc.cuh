@@ -35,7 +35,8 @@ namespace attn_tc {
 using attn::DH; using attn::QTILE; using attn::KTILE; using attn::SCALE; using attn::SCALE_LOG2; using attn::LOG2E; using attn::LN2;
 
 // barriers in the control area, from byte 832: q_full | st_full[3] | st_empty[3] | a_full[2] | a_free[2] | w_full[2] |
-// b_full[2] | b_free[2] | done | st2_full[2] | st2_empty[2] (the dK/dV task's two-stage ring)      (22 x 8 B)
+// b_full[2] | b_free[2] (reserved: no task waits on it since the forward output accumulates in tensor memory) | done |
+// st2_full[2] | st2_empty[2] (the dK/dV task's two-stage ring)      (22 x 8 B)
 constexpr int BAR0 = 832;
 enum { B_QFULL = 0, B_STFULL = 1, B_STEMPTY = 4, B_AFULL = 7, B_AFREE = 9, B_WFULL = 11, B_BFULL = 13, B_BFREE = 15, B_DONE = 17, B_ST2FULL = 18, B_ST2EMPTY = 20, NBAR = 22 };
 static_assert(BAR0 + 8 * NBAR <= CTRL_BYTES, "attention barriers do not fit the control area");
