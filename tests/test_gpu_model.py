@@ -209,3 +209,20 @@ def test_checkpoint_resume_continues_bit_for_bit(ofa, oracle, tmp_path):
     ofa.files.write_loss_log(tmp_path / "loss.txt", la)
     assert (tmp_path / "loss.txt").read_text().splitlines()[0] == "0 %.6f" % la[0]
     c.close()
+
+
+def test_phase_windows_follow_the_dependency_chain(ofa, oracle):
+    """ofa_phase_window: in the last step of a launch every phase with tasks has first <= last, and a phase starts no earlier than the
+    phases it depends on within the step started (the reference's "phase wall-clock at step" table, ofa.cu:735-743)."""
+    ocfg, w0, tokens, starts, mk = tiny_setup(ofa, oracle, nsteps=3)
+    mk.run(3)
+    win = mk.phase_windows(); ph = mk.phases()
+    names = [p["name"] for p in ph]
+    none = 0xFFFFFFFFFFFFFFFF
+    assert all(a != none and a <= b for a, b in win)
+    for i in range(len(ph)):
+        for dep, delta in mk.phase_deps(i):
+            if delta == 0:
+                # the dependency's last task ended before this phase's first began (its end stamp is read just after it signals: 5 us of slack)
+                assert win[dep][1] <= win[i][0] + 5000, (names[dep], names[i])
+    mk.close()
