@@ -13,7 +13,7 @@ def plan(ofa, preset, **kw):
 
 
 @pytest.mark.parametrize("preset,kw", [("gpt_s", {}), ("gpt_s", dict(tied_head=1)), ("gpt_s", dict(mode=1)), ("gpt_s", dict(mode=2)),
-                                       ("gpt_s", dict(dp_world=8, grad_bf16=1, ext_sync=1)), ("gpt_s", dict(adam_interleave=1, head_dx_splitk=1)), ("tiny", {}), ("tiny", dict(tied_head=1)), ("tiny", dict(mode=2))])
+                                       ("gpt_s", dict(dp_world=8, grad_bf16=1, ext_sync=1)), ("gpt_s", dict(adam_interleave=1, head_dx_splitk=1)), ("gpt_s", dict(adam_interleave=12)), ("tiny", {}), ("tiny", dict(tied_head=1)), ("tiny", dict(mode=2))])
 def test_training_graph_is_topologically_ordered(ofa, preset, kw):
     mk = plan(ofa, preset, **kw)
     ph = mk.phases()
@@ -109,3 +109,26 @@ def test_planning_context_cannot_touch_a_device(ofa):
     with pytest.raises(ofa.OfaError):
         mk.load_weights(np.zeros(mk.num_params, np.float32))
     mk.close()
+
+
+def test_trickled_adamw_covers_every_parameter_once(ofa):
+    """cfg.adam_interleave = n >= 2 cuts the optimizer phases into chunks spread through the backward pass: the chunks of a group
+    must add up to the group's tasks, and the group's usual name must wait for all of them."""
+    base = plan(ofa, "gpt_s"); tr = plan(ofa, "gpt_s", adam_interleave=12)
+    pb, pt = base.phases(), tr.phases()
+    K_ADAMW = 13
+    count = lambda ph: sum(p["ntasks"] for p in ph if p["kind"] == K_ADAMW)
+    assert count(pb) == count(pt)
+    names = [p["name"] for p in pt]
+    for group in ["adamw head"] + [f"adamw L{l}" for l in range(1, 12)]:
+        parts = [i for i, n in enumerate(names) if n.startswith(group + " .")]
+        assert len(parts) >= 2
+        whole = next(p["ntasks"] for p in pb if p["name"] == group)
+        assert sum(pt[i]["ntasks"] for i in parts) == whole
+        deps = {d for d, delta in tr.phase_deps(names.index(group)) if delta == 0}
+        assert deps == set(parts)                                          # the join phase waits for every chunk
+        ready = names.index(group + " ready")
+        for i in parts:
+            assert tr.phase_deps(i) == [(ready, 0)]
+    assert "adamw L0 .0" not in names and "adamw L0" in names             # nothing left to spread the last group into
+    base.close(); tr.close()
