@@ -193,6 +193,8 @@ def main():
         cfg.dp_world, cfg.grad_bf16, cfg.ext_sync = world, 1, 1
     for kv in args.cfg:
         k, v = kv.split("=")
+        if k not in [f[0] for f in cfg._fields_]:
+            raise SystemExit(f"--cfg: ofa_config has no field {k!r}")
         setattr(cfg, k, int(v))
     mk = ofa.Megakernel(cfg)
     mk.load_weights(init_flat(mk))
