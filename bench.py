@@ -214,9 +214,9 @@ def main():
         mk.launch(n)
         if dp is not None:
             dp.enqueue(n)                              # after the launch: a stream wait must never sit in front of the kernel that satisfies it
-        mk.wait(600000)
-        if dp is not None:
-            dp.finish()
+            dp.wait(600000)                            # kernel + communication queue; a rank that stopped early makes every rank raise
+        else:
+            mk.wait(600000)
         return mk.last_launch_ms
 
     run(W)

@@ -69,7 +69,7 @@ typedef struct {
   int device;               /* CUDA device ordinal; < 0 = planning context: layout, buckets and phase graphs are built and can be queried, nothing touches a device and nothing can be launched */
 } ofa_config;
 
-/* preset: "tiny" (BASELINE config 1) or "gpt_s" (config 2). */
+/* preset: "tiny" (the char-level fp32 model: vocab 65, d_model 64, 2 layers, 4 heads, context 64, batch 16) or "gpt_s" (the 162M bf16 model: vocab 50304 untied, d_model 768, 12 layers, 12 heads, context 1024, batch 4). */
 int ofa_default_config(ofa_config* cfg, const char* preset);
 
 /* lifecycle: replaces the body of main() up to the launch (ofa.cu:415-707). One ctx per device. */
@@ -90,7 +90,8 @@ int ofa_read_adam_m(ofa_ctx* ctx, float* out, size_t n);
 int ofa_read_adam_v(ofa_ctx* ctx, float* out, size_t n);
 int ofa_load_adam_state(ofa_ctx* ctx, const float* m, const float* v, size_t n, int step_base);   /* resume */
 
-/* tokens: replaces --data / --starts (ofa.cu:513-528). starts is [nsteps][batch] window offsets, or NULL for hashed starts. */
+/* tokens: replaces --data / --starts (ofa.cu:513-528). starts is [nsteps][batch] window offsets, or NULL for hashed starts.
+ * ofa_set_tokens drops a starts table set earlier (it was checked against the old stream): set tokens first, then starts. */
 int ofa_set_tokens(ofa_ctx* ctx, const uint32_t* tokens, size_t n);
 int ofa_set_starts(ofa_ctx* ctx, const uint32_t* starts, size_t nsteps);
 
@@ -174,6 +175,11 @@ int ofa_d2h(void* dst, const void* src, size_t bytes);
  * = {lr, beta1, beta2, eps, wd, grad_scale} with optimizer step r+1. */
 int ofa_run_phases(int dtype, const ofa_dims* dims, const ofa_phase* phases, int nph, int repeats, const float* adam,
                    float* ms, ofa_status_t* status);
+/* Test hook: with seed != 0 every phase uploaded afterwards (by ofa_launch or ofa_run_phases, training and serving graphs) hands
+ * its tasks out in a pseudo-randomly permuted order; 0 restores the natural order. Every result must be bit-identical either
+ * way: the reference checks its task libraries the same way (llm/gemm/test_gemm.cu:20-49, llm/attention/test_attention.cu:45-77,
+ * llm/decode/test_decode.cu:135-158 pull tasks in shuffled orders). Process-global, not for production use. */
+void ofa_debug_set_task_shuffle(unsigned seed);
 
 /* ---- allocation-free entry point ------------------------------------------------------------------------------------
  * No counterpart in the reference (its program allocates everything up front in main()). LayerNorm backward for the bf16

@@ -91,6 +91,7 @@ PROTOTYPES = {
     "ofa_ln_bwd_noalloc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "ofa_noalloc_max_rows": (C.c_int, []),
     "ofa_noalloc_last_error": (C.c_char_p, []),
+    "ofa_debug_set_task_shuffle": (None, [C.c_uint]),
     "ofa_run_phases": (C.c_int, [C.c_int, C.POINTER(Dims), C.POINTER(Phase), C.c_int, C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(Status)]),
 }
 

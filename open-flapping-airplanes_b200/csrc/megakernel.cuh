@@ -248,7 +248,7 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
     __syncthreads();
   }
   u64 waited = 0, t_claim = 0, t_sync = 0, t_tail = 0, tl0 = 0, tl1 = 0;   // thread 0: where the time outside tasks goes
-  int c_ph = -1, c_lo = 0, c_hi = 0;                 // thread 0: cached phase and its ticket range [c_lo, c_hi) within a step
+  int c_ph = -1, c_lo = 0, c_hi = 0, c_mul = 0;      // thread 0: cached phase, its ticket range [c_lo, c_hi) within a step, and its test-only task permutation
   unsigned next_g = 0; bool have_next = false; unsigned claims = 0;   // thread 0: the ticket taken at the end of the previous task
   for (;;) {
     if (tid == 0) {                                  // ---- claim (and, for the training job, wait for the dependencies)
@@ -267,13 +267,16 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
           // A block's tickets grow, so within a step it only moves forward through the phases: keep the current phase's
           // ticket range in registers and walk on, one scheduling record per phase passed. The record of the phase after
           // the one just worked on was requested at the end of the previous task and is normally already in shared memory.
-          if (r < c_lo) { c_ph = -1; c_lo = 0; c_hi = 0; }        // a new step
+          if (r < c_lo) { c_ph = -1; c_lo = 0; c_hi = 0; c_mul = 0; }        // a new step
           while (r >= c_hi) {
             c_ph++;
             need_rec(c_ph);
-            c_lo = s_rec[0]; c_hi = s_rec[1];
+            c_lo = s_rec[0]; c_hi = s_rec[1]; c_mul = s_rec[3];
           }
           ph = c_ph; local = r - c_lo;
+          // test hook (SchedRec::perm_mul, 0 in production): tickets of a phase are handed out in a permuted task order, which
+          // must not change any result - the reference's shuffled-order check (llm/gemm/test_gemm.cu:20-49)
+          if (c_mul) local = (int)(((long long)local * c_mul + (c_mul >> 1)) % (long long)(c_hi - c_lo));
           if (job_id == 0 && !(step == rstep && ph == rph)) {
             const u64 w0 = gtimer();
             need_rec(ph);

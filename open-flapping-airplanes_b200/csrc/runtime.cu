@@ -19,6 +19,19 @@ using namespace ofa;
 namespace {
 
 thread_local std::string g_create_error;
+unsigned g_task_shuffle_seed = 0;   // test hook (ofa_debug_set_task_shuffle): != 0 -> the tickets of every phase uploaded from now on run their tasks in a permuted order
+
+int gcd_int(int a, int b) { while (b) { const int t = a % b; a = b; b = t; } return a; }
+// multiplier in [2, n) coprime with n (0 = identity for phases too small to permute)
+int shuffle_multiplier(unsigned seed, int phase, int n) {
+  if (!seed || n < 3) return 0;
+  int a = (int)((seed * 2654435761u + (unsigned)phase * 40503u) % (unsigned)n);
+  for (int tries = 0; tries < n; tries++, a++) {
+    if (a >= n) a = 2;
+    if (a >= 2 && gcd_int(a, n) == 1) return a;
+  }
+  return 0;
+}
 
 struct HostPhase { std::string name; PhaseDesc d; std::vector<Dep> deps; };
 
@@ -182,6 +195,7 @@ bool upload_job(const std::vector<HostPhase>& ph, int last_phase, int nsteps, De
     r.lo = prefix[i]; r.hi = prefix[i + 1];
     const int n = (int)ph[i].deps.size();
     r.ndeps = n <= 4 ? n : -1;
+    r.perm_mul = shuffle_multiplier(g_task_shuffle_seed, i, nt[i]);
     for (int k = 0; k < n && n <= 4; k++) { r.dep[3 * k] = ph[i].deps[k].phase; r.dep[3 * k + 1] = ph[i].deps[k].delta; r.dep[3 * k + 2] = nt[ph[i].deps[k].phase]; }
   }
   if (deps.empty()) deps.push_back(Dep{0, 0});
@@ -215,6 +229,23 @@ template <class T, int D, int DH> cudaError_t launch_kernel(const Ctx& C, int nb
   cudaFuncSetAttribute(ofa_kernel<T, D, DH>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
   ofa_kernel<T, D, DH><<<nblocks, NTHR, smem, s>>>(C);
   return cudaGetLastError();
+}
+
+// Tasks whose shared-memory need grows with the batch or the context must fit the block's task area: on the bf16 path that is
+// the fixed GEMM pipeline + staging region below the control area (an oversize task would overwrite the block's barriers and
+// scheduler words, or store beyond the shared window); on the fp32 path the window is sized from them and must stay within
+// the device's per-block opt-in limit. Returns an empty string when everything fits.
+std::string smem_fit_error(bool bf, int Tctx, int N, bool emb_wte, bool decode, int smem) {
+  if (bf) {
+    const size_t room = gemm_tc::BAR_OFFSET;
+    if (emb_wte && ew::embed_bwd_wte_smem_bytes(N) > room)
+      return "batch * ctx_len = " + std::to_string(N) + " tokens: the embedding-backward task needs " + std::to_string(ew::embed_bwd_wte_smem_bytes(N)) + " B of shared memory, the block has " + std::to_string(room);
+    if (decode && dec::smem_bytes<bf16, 768, 64>(Tctx) > room)
+      return "ctx_len " + std::to_string(Tctx) + ": the serving tasks need " + std::to_string(dec::smem_bytes<bf16, 768, 64>(Tctx)) + " B of shared memory, the block has " + std::to_string(room);
+    return "";
+  }
+  if (smem > 227 * 1024) return "the fp32 path would need " + std::to_string(smem) + " B of shared memory per block (limit 232,448)";
+  return "";
 }
 
 int smem_for(bool bf, int Tctx, int N) {
@@ -257,6 +288,8 @@ struct ofa_ctx {
   std::vector<Span> buckets;
   cudaStream_t stream = nullptr, abort_stream = nullptr; cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   bool dry = false;
+  int step_done_cap = 0; size_t starts_cap = 0, tokens_cap = 0;
+  bool abort_requested = false;      // ofa_abort was called for the launch in flight (also honoured if the device word was cleared by a launch that had not started yet)
   bool in_flight = false; int steps_total = 0, last_nsteps = 0; float last_ms = 0.f; int dec_steps_total = 0;
   std::string err;
 };
@@ -734,13 +767,17 @@ extern "C" int ofa_default_config(ofa_config* cfg, const char* preset) {
 extern "C" const char* ofa_last_error(const ofa_ctx* ctx) { return ctx ? ctx->err.c_str() : g_create_error.c_str(); }
 
 // Host-requested abort: raises the grid-wide abort word; every bounded wait on the device sees it and the kernel returns.
+static void post_abort(ofa_ctx* c) {
+  static const int one = 1;
+  if (!c->abort_stream) cudaStreamCreateWithFlags(&c->abort_stream, cudaStreamNonBlocking);
+  cudaMemcpyAsync(&c->d_status->abort, &one, sizeof(int), cudaMemcpyHostToDevice, c->abort_stream);
+}
 extern "C" int ofa_abort(ofa_ctx* c) {
   if (!c || c->dry) return OFA_BAD_ARGUMENT;
   if (!c->in_flight) return OFA_NOT_LAUNCHED;
   cudaSetDevice(c->device);
-  static const int one = 1;
-  if (!c->abort_stream) cudaStreamCreateWithFlags(&c->abort_stream, cudaStreamNonBlocking);
-  cudaMemcpyAsync(&c->d_status->abort, &one, sizeof(int), cudaMemcpyHostToDevice, c->abort_stream);
+  c->abort_requested = true;
+  post_abort(c);
   return OFA_OK;
 }
 
@@ -752,10 +789,13 @@ extern "C" void ofa_destroy(ofa_ctx* c) {
     // never block forever: ask the kernel to drain, give it a few seconds, and otherwise leak the device memory it may still use
     ofa_abort(c);
     bool done = false;
-    for (int i = 0; i < 25000 && !done; i++) { done = cudaEventQuery(c->ev1) != cudaErrorNotReady; if (!done) { struct timespec sl = {0, 200000}; nanosleep(&sl, nullptr); } }
+    for (int i = 0; i < 25000 && !done; i++) { done = cudaEventQuery(c->ev1) != cudaErrorNotReady; if (!done) { if (i % 64 == 63) post_abort(c); struct timespec sl = {0, 200000}; nanosleep(&sl, nullptr); } }
     if (!done) { delete c; return; }
   }
   c->train_job.free_all(); c->dec_job.free_all();
+  if (c->d_step_done) cudaFree(c->d_step_done);
+  if (c->d_tokens) cudaFree(c->d_tokens);
+  if (c->d_starts) cudaFree(c->d_starts);
   c->ar.free_all();
   if (c->h_live) cudaFreeHost(c->h_live);
   if (c->h_out) cudaFreeHost(c->h_out);
@@ -805,6 +845,10 @@ extern "C" int ofa_create(const ofa_config* cfg, ofa_ctx** out) {
   }
   c->nblocks = 2 * c->num_sms;
   c->smem = smem_for(c->bf, m.T, m.N);
+  {
+    const std::string e = smem_fit_error(c->bf, m.T, m.N, cfg->mode != OFA_MODE_FORWARD && cfg->mode != OFA_MODE_DECODE_ONLY, cfg->use_decode != 0, c->smem);
+    if (!e.empty()) return bail(OFA_BAD_CONFIG, e);
+  }
   if (!dry) {
     if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess) return bail(OFA_CUDA_ERROR, "stream");
     cudaEventCreate(&c->ev0); cudaEventCreate(&c->ev1);
@@ -895,21 +939,25 @@ extern "C" int ofa_read_adam_v(ofa_ctx* c, float* out, size_t n) { return c ? re
 extern "C" int ofa_read_grads(ofa_ctx* c, float* out, size_t n) {
   if (!c) return OFA_BAD_ARGUMENT;
   if (!c->cfg.grad_bf16) return read_f32(c, c->G32, out, n);
+  if (c->dry) return fail(c, OFA_BAD_ARGUMENT, "planning context (device < 0) has no device memory");
   if (!out || n > c->lay.total) return fail(c, OFA_BAD_ARGUMENT, "bad size");
   if (c->in_flight) return fail(c, OFA_BAD_ARGUMENT, "launch in flight: call ofa_wait first");
   cudaSetDevice(c->device);
   float* tmp = nullptr;
   if (cudaMalloc(&tmp, n * sizeof(float)) != cudaSuccess) return fail(c, OFA_CUDA_ERROR, "cudaMalloc failed");
   bf16_to_f32_kernel<<<1024, 256>>>(c->Gbf, tmp, n);
-  const cudaError_t e = cudaMemcpy(out, tmp, n * sizeof(float), cudaMemcpyDeviceToHost);
+  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) e = cudaMemcpy(out, tmp, n * sizeof(float), cudaMemcpyDeviceToHost);
   cudaFree(tmp);
   return e == cudaSuccess ? OFA_OK : fail(c, OFA_CUDA_ERROR, cudaGetErrorString(e));
 }
 extern "C" int ofa_load_adam_state(ofa_ctx* c, const float* mm, const float* vv, size_t n, int step_base) {
+  if (c && c->dry) return fail(c, OFA_BAD_ARGUMENT, "planning context (device < 0) has no device memory");
   if (!c || !mm || !vv || n != c->lay.total || step_base < 0) return fail(c, OFA_BAD_ARGUMENT, "bad optimizer state");
   if (c->in_flight) return fail(c, OFA_BAD_ARGUMENT, "launch in flight");
   cudaSetDevice(c->device);
-  cudaMemcpy(c->M32, mm, n * sizeof(float), cudaMemcpyHostToDevice); cudaMemcpy(c->V32, vv, n * sizeof(float), cudaMemcpyHostToDevice);
+  if (cudaMemcpy(c->M32, mm, n * sizeof(float), cudaMemcpyHostToDevice) != cudaSuccess || cudaMemcpy(c->V32, vv, n * sizeof(float), cudaMemcpyHostToDevice) != cudaSuccess)
+    return fail(c, OFA_CUDA_ERROR, std::string("H2D failed: ") + cudaGetErrorString(cudaGetLastError()));
   c->steps_total = step_base;
   return OFA_OK;
 }
@@ -920,19 +968,30 @@ extern "C" int ofa_set_tokens(ofa_ctx* c, const uint32_t* tokens, size_t n) {
   if (c->in_flight) return fail(c, OFA_BAD_ARGUMENT, "launch in flight");
   for (size_t i = 0; i < n; i++) if (tokens[i] >= (uint32_t)c->md.V) return fail(c, OFA_BAD_ARGUMENT, "token id out of range");
   cudaSetDevice(c->device);
-  if (n > c->ntok || !c->d_tokens) { c->d_tokens = c->ar.alloc<uint32_t>(n, false); if (!c->d_tokens) return fail(c, OFA_CUDA_ERROR, "out of device memory"); }
+  if (n > c->tokens_cap) {                          // one buffer, grown when needed (the old one is freed)
+    if (c->d_tokens) cudaFree(c->d_tokens);
+    c->d_tokens = nullptr; c->tokens_cap = 0; c->ntok = 0;
+    if (cudaMalloc(&c->d_tokens, n * 4) != cudaSuccess) return fail(c, OFA_CUDA_ERROR, "out of device memory");
+    c->tokens_cap = n;
+  }
   c->ntok = n;
+  c->nstarts = 0;                                   // a starts table was validated against the old stream: it has to be set again
   return cudaMemcpy(c->d_tokens, tokens, n * 4, cudaMemcpyHostToDevice) == cudaSuccess ? OFA_OK : fail(c, OFA_CUDA_ERROR, "H2D failed");
 }
 extern "C" int ofa_set_starts(ofa_ctx* c, const uint32_t* starts, size_t nsteps) {
   if (!c) return OFA_BAD_ARGUMENT;
+  if (c->dry) return fail(c, OFA_BAD_ARGUMENT, "planning context (device < 0) has no device memory");
   if (c->in_flight) return fail(c, OFA_BAD_ARGUMENT, "launch in flight");
-  if (!starts || nsteps == 0) { c->d_starts = nullptr; c->nstarts = 0; return OFA_OK; }
+  if (!starts || nsteps == 0) { c->nstarts = 0; return OFA_OK; }
   const size_t n = nsteps * c->md.B;
   for (size_t i = 0; i < n; i++) if ((size_t)starts[i] + c->md.T + 1 > c->ntok) return fail(c, OFA_BAD_ARGUMENT, "start offset beyond the token stream (set tokens first)");
   cudaSetDevice(c->device);
-  c->d_starts = c->ar.alloc<uint32_t>(n, false);
-  if (!c->d_starts) return fail(c, OFA_CUDA_ERROR, "out of device memory");
+  if (n > c->starts_cap) {
+    if (c->d_starts) cudaFree(c->d_starts);
+    c->d_starts = nullptr; c->starts_cap = 0; c->nstarts = 0;
+    if (cudaMalloc(&c->d_starts, n * 4) != cudaSuccess) return fail(c, OFA_CUDA_ERROR, "out of device memory");
+    c->starts_cap = n;
+  }
   c->nstarts = (int)nsteps;
   return cudaMemcpy(c->d_starts, starts, n * 4, cudaMemcpyHostToDevice) == cudaSuccess ? OFA_OK : fail(c, OFA_CUDA_ERROR, "H2D failed");
 }
@@ -954,8 +1013,13 @@ extern "C" int ofa_launch(ofa_ctx* c, int nsteps) {
       if (c->d_loss_hist) cudaMemcpy(nl, c->d_loss_hist, sizeof(float) * c->loss_cap, cudaMemcpyDeviceToDevice);
       c->d_loss_hist = nl; c->loss_cap = cap;
     }
-    c->d_step_done = c->ar.alloc<unsigned long long>(nsteps);
-    if (!c->d_step_done) return fail(c, OFA_CUDA_ERROR, "out of device memory");
+    if (nsteps > c->step_done_cap) {               // grown, never re-allocated per launch: a loop of short launches must not leak
+      if (c->d_step_done) cudaFree(c->d_step_done);
+      c->d_step_done = nullptr; c->step_done_cap = 0;
+      const int cap = std::max(1024, 2 * nsteps);
+      if (cudaMalloc(&c->d_step_done, sizeof(unsigned long long) * cap) != cudaSuccess) return fail(c, OFA_CUDA_ERROR, "out of device memory");
+      c->step_done_cap = cap;
+    }
   }
   if (c->cfg.use_decode) {
     const int dsteps = train_on ? (1 << 20) : nsteps;
@@ -965,12 +1029,19 @@ extern "C" int ofa_launch(ofa_ctx* c, int nsteps) {
   C.use_train = train_on ? 1 : 0;
   if (train_on) C.train = c->train_job.j;
   if (c->cfg.use_decode) C.dec = c->dec_job.j;
-  C.data = c->d_tokens; C.ntok = c->ntok; C.starts = c->d_starts; C.nstarts = c->nstarts;
+  C.data = c->d_tokens; C.ntok = c->ntok; C.starts = c->nstarts > 0 ? c->d_starts : nullptr; C.nstarts = c->nstarts;
   C.loss_hist = c->d_loss_hist ? c->d_loss_hist + c->steps_total : nullptr;   // history, LR schedule and data windows continue across launches
   C.step_done = c->d_step_done;
   C.step_base = c->steps_total;
+  c->abort_requested = false;
   cudaMemsetAsync(c->d_status, 0, sizeof(DevStatus), c->stream);
   cudaMemsetAsync(c->d_finished, 0, 2 * sizeof(int), c->stream);
+  if (c->cfg.use_decode) {
+    // The serving blocks of the previous launch left when training finished, normally in the middle of a token: the residual then
+    // holds the contributions of some layers. The token is decoded again from layer 0 (the serving job's counters restart), so the
+    // residual is rebuilt from the token and position the last completed sample step stored; K/V rows, q and candidates are rewritten.
+    if (c->bf) decode_init_embed_kernel<bf16, 768><<<1, NTHR, 0, c->stream>>>(c->C.dp); else decode_init_embed_kernel<float, 64><<<1, NTHR, 0, c->stream>>>(c->C.dp);
+  }
   C.arrived = c->d_finished + 1;
   cudaMemsetAsync(c->d_phase_busy, 0, sizeof(unsigned long long) * 2 * std::max<size_t>(1, c->train_ph.size()), c->stream);
   cudaMemsetAsync(c->d_blk_busy, 0, sizeof(unsigned long long) * 6 * c->nblocks, c->stream);
@@ -995,6 +1066,7 @@ extern "C" int ofa_wait(ofa_ctx* c, int timeout_ms, ofa_status_t* status) {
   if (!c->in_flight) { if (status) status->code = OFA_NOT_LAUNCHED; return fail(c, OFA_NOT_LAUNCHED, "nothing in flight"); }
   cudaSetDevice(c->device);
   struct timespec ts0; clock_gettime(CLOCK_MONOTONIC, &ts0);
+  unsigned polls = 0;
   for (;;) {
     cudaError_t q = cudaEventQuery(c->ev1);
     if (q == cudaSuccess) break;
@@ -1002,6 +1074,8 @@ extern "C" int ofa_wait(ofa_ctx* c, int timeout_ms, ofa_status_t* status) {
     struct timespec ts; clock_gettime(CLOCK_MONOTONIC, &ts);
     const double ms = (ts.tv_sec - ts0.tv_sec) * 1e3 + (ts.tv_nsec - ts0.tv_nsec) * 1e-6;
     if (timeout_ms >= 0 && ms > timeout_ms) { if (status) status->code = OFA_TIMEOUT; return OFA_TIMEOUT; }
+    // an abort requested before the launch's own set-up ran may have been cleared by it: keep posting it while the launch lives
+    if (c->abort_requested && (++polls % 64) == 0) post_abort(c);
     struct timespec sl = {0, 200000}; nanosleep(&sl, nullptr);
   }
   c->in_flight = false;
@@ -1136,15 +1210,22 @@ extern "C" int ofa_run_phases(int dtype, const ofa_dims* dims, const ofa_phase* 
   if (status) memset(status, 0, sizeof *status);
   if (!dims || !phases || nph <= 0 || repeats <= 0 || (dtype != OFA_DTYPE_BF16 && dtype != OFA_DTYPE_F32)) return fail(nullptr, OFA_BAD_ARGUMENT, "bad argument");
   const bool bf = dtype == OFA_DTYPE_BF16;
-  int dev = 0; cudaDeviceProp prop;
-  if (cudaGetDevice(&dev) != cudaSuccess || cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return fail(nullptr, OFA_CUDA_ERROR, "no CUDA device");
-  if (prop.major != 10) return fail(nullptr, OFA_CUDA_ERROR, "sm_100a code only");
   ModelDims m{};
   m.V = dims->vocab; m.D = dims->d_model; m.L = dims->n_layer; m.H = dims->n_head; m.T = dims->ctx_len; m.B = dims->batch; m.N = m.B * m.T; m.FF = 4 * m.D;
   m.DH = m.H > 0 ? m.D / m.H : 0; m.valid_vocab = m.V;
+  if (m.V <= 0 || m.H <= 0 || m.T <= 0 || m.B <= 0) return fail(nullptr, OFA_BAD_CONFIG, "non-positive dimension");
   if (bf ? (m.D != 768 || m.DH != 64) : (m.D != 64 || m.DH != 16)) return fail(nullptr, OFA_BAD_CONFIG, "unsupported width / head dim for this dtype");
-  const int nblocks = 2 * prop.multiProcessorCount;
   const int smem = smem_for(bf, m.T, m.N);
+  {  // sizes that do not fit a block are refused before anything touches the device
+    bool emb = false;
+    for (int i = 0; i < nph; i++) emb = emb || phases[i].kind == TK_EMB_WTE;
+    const std::string e = smem_fit_error(bf, m.T, m.N, emb, false, smem);
+    if (!e.empty()) return fail(nullptr, OFA_BAD_CONFIG, e);
+  }
+  int dev = 0; cudaDeviceProp prop;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return fail(nullptr, OFA_CUDA_ERROR, "no CUDA device");
+  if (prop.major != 10) return fail(nullptr, OFA_CUDA_ERROR, "sm_100a code only");
+  const int nblocks = 2 * prop.multiProcessorCount;
   Arena ar; DevJob dj; std::string err;
   std::vector<HostPhase> P(nph);
   for (int i = 0; i < nph; i++) {
@@ -1217,6 +1298,10 @@ extern "C" int ofa_run_phases(int dtype, const ofa_dims* dims, const ofa_phase* 
   ar.free_all(); dj.free_all();
   return rc;
 }
+
+// Test hook: seed != 0 makes every phase uploaded afterwards (ofa_launch, ofa_run_phases) hand its tasks out in a permuted order;
+// 0 restores the natural order. Results must be bit-identical either way (llm/gemm/test_gemm.cu:20-49 checks the same property).
+extern "C" void ofa_debug_set_task_shuffle(unsigned seed) { g_task_shuffle_seed = seed; }
 
 // ================================================================================================ C ABI: data-parallel hooks
 extern "C" int ofa_num_buckets(const ofa_ctx* c) { return c ? (int)c->buckets.size() : 0; }

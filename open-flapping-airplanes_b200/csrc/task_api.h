@@ -79,7 +79,7 @@ struct Dep { int phase; int delta; };   // need done[phase] >= ntasks[phase] * (
 struct alignas(16) SchedRec {
   int lo, hi;               // tickets [lo, hi) of a step belong to this phase
   int ndeps;                // 0..4 dependencies held in dep[]; -1: more than four, use Job::deps
-  int pad;
+  int perm_mul;             // 0 (production), or a multiplier coprime with the task count: ticket i of the phase runs task (i * perm_mul + perm_mul / 2) % ntasks (test hook: results must not depend on the order)
   int dep[12];              // per dependency: phase, step delta, task count of that phase
 };
 constexpr int CTRL_BYTES = 1024;   // control area at the end of every block's dynamic shared memory

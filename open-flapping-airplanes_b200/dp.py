@@ -15,8 +15,19 @@ Two rules keep this free of false dependencies:
   * NCCL's blocks run on the SMs the megakernel leaves unoccupied (the reserved partition), so the number of NCCL channels
     must not exceed what fits there: `configure_env()` caps it before the process group is created.
 If the communication side never answers, the device-side wait expires and the launch returns OFA_DEVICE_ABORT.
+
+The reverse case - a rank's kernel stops early (a bounded device wait expired, or the host called ofa_abort) - would leave that
+rank's queued stream waits without the `ready` values they wait for, and every peer's all-reduce waiting for this rank.
+`DataParallel.wait()` handles it: the failing rank raises every ready flag to the last queued target (`cancel()`), so its queue
+drains and the collectives complete with data nobody will use; afterwards the ranks exchange their status, so that every rank
+raises, not only the one whose kernel stopped. `finish()` gives up after a timeout instead of blocking for good.
+
+The queue itself sits behind a small interface (wait for a flag value, all-reduce a span, write a flag value, raise the ready
+flags out of band, drain with a timeout). `CudaFlagQueue` implements it with stream memory operations; `HostFlagQueue` runs
+the same operations on a host thread over a numpy flag array, so the cancel and status logic is tested among CPU ranks (gloo).
 """
 import os
+import time
 
 import numpy as np
 
@@ -65,14 +76,17 @@ class _DevArray:
         self.__cuda_array_interface__ = {"shape": (n,), "typestr": typestr, "data": (int(ptr), False), "version": 3, "strides": None}
 
 
-class DataParallel:
+class DataParallelAborted(RuntimeError):
+    """A rank's kernel stopped before the end of the launch; raised on EVERY rank of the group after the queues have drained."""
+
+
+class CudaFlagQueue:
+    """The communication queue on a CUDA stream: stream memory operations on the library's device flags around NCCL calls."""
+
     def __init__(self, mk, dist, stream=None):
         import torch
         from cuda.bindings import driver as cu
-        self.torch, self.cu, self.mk, self.dist = torch, cu, mk, dist
-        self.buckets = mk.buckets()
-        if not self.buckets:
-            raise RuntimeError("the context was not created with ext_sync=1")
+        self.torch, self.cu, self.dist = torch, cu, dist
         n = mk.num_params
         gptr = mk.grad_buffer_ptr()
         if mk.cfg.grad_bf16:
@@ -84,6 +98,7 @@ class DataParallel:
             raise RuntimeError("torch copied the gradient buffer instead of aliasing it")
         self.ready_ptr, self.done_ptr = mk.ext_flags_ptrs()
         self.stream = stream if stream is not None else torch.cuda.Stream()
+        self.side = torch.cuda.Stream()                  # out-of-band flag writes (cancel) must not queue behind the waits they release
         # first collective on the communication stream now: communicator set-up and its allocations must not happen while
         # a persistent kernel is resident
         with torch.cuda.stream(self.stream):
@@ -96,18 +111,151 @@ class DataParallel:
         if int(err) != 0:
             raise RuntimeError(f"CUDA driver call failed: {err}")
 
+    def wait_ready(self, b, value):
+        self._check(self.cu.cuStreamWaitValue32(self.cu.CUstream(self.stream.cuda_stream), self.ready_ptr + 4 * b, value,
+                                                self.cu.CUstreamWaitValue_flags.CU_STREAM_WAIT_VALUE_GEQ))
+
+    def all_reduce(self, off, cnt):
+        with self.torch.cuda.stream(self.stream):
+            self.dist.all_reduce(self.grad[off:off + cnt])
+
+    def write_done(self, b, value):
+        self._check(self.cu.cuStreamWriteValue32(self.cu.CUstream(self.stream.cuda_stream), self.done_ptr + 4 * b, value, 0))
+
+    def raise_ready(self, nbuckets, value):
+        h = self.cu.CUstream(self.side.cuda_stream)
+        for b in range(nbuckets):
+            self._check(self.cu.cuStreamWriteValue32(h, self.ready_ptr + 4 * b, value, 0))
+
+    def drain(self, timeout_s):
+        t0 = time.monotonic()
+        while not self.stream.query():
+            if timeout_s is not None and time.monotonic() - t0 > timeout_s:
+                return False
+            time.sleep(0.0005)
+        return True
+
+    def exchange_failed(self, failed):
+        t = self.torch.tensor([1 if failed else 0], device="cuda", dtype=self.torch.int32)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return bool(t.item())
+
+
+class HostFlagQueue:
+    """The same queue on the host: a worker thread executes the operations in order over a numpy flag array (ready[0:32],
+    done[32:64]) and a CPU gradient tensor, with torch.distributed (gloo) as the collective. Stands in for the device flags
+    and the stream in CPU tests; the "kernel" of such a test is whoever writes ready[] and reads done[]."""
+
+    def __init__(self, grad, dist, poll_s=0.0005):
+        import threading
+        self.grad, self.dist, self.poll_s = grad, dist, poll_s
+        self.flags = np.zeros(64, dtype=np.int32)
+        self.ops, self.lock, self.stop = [], threading.Lock(), False
+        self.idle = threading.Event(); self.idle.set()
+        self.th = threading.Thread(target=self._run, daemon=True); self.th.start()
+
+    def _run(self):
+        while not self.stop:
+            with self.lock:
+                op = self.ops.pop(0) if self.ops else None
+                if op is None:
+                    self.idle.set()
+            if op is None:
+                time.sleep(self.poll_s); continue
+            kind = op[0]
+            if kind == "wait":
+                while self.flags[op[1]] < op[2] and not self.stop:
+                    time.sleep(self.poll_s)
+            elif kind == "reduce":
+                self.dist.all_reduce(self.grad[op[1]:op[1] + op[2]])
+            else:
+                self.flags[32 + op[1]] = op[2]
+
+    def _push(self, op):
+        with self.lock:
+            self.idle.clear(); self.ops.append(op)
+
+    def wait_ready(self, b, value):
+        self._push(("wait", b, value))
+
+    def all_reduce(self, off, cnt):
+        self._push(("reduce", off, cnt))
+
+    def write_done(self, b, value):
+        self._push(("write", b, value))
+
+    def raise_ready(self, nbuckets, value):
+        for b in range(nbuckets):
+            self.flags[b] = max(int(self.flags[b]), value)
+
+    def drain(self, timeout_s):
+        return self.idle.wait(timeout_s)
+
+    def exchange_failed(self, failed):
+        import torch
+        t = torch.tensor([1 if failed else 0], dtype=torch.int32)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return bool(t.item())
+
+    def close(self):
+        self.stop = True
+
+
+class DataParallel:
+    def __init__(self, mk, dist, stream=None, queue=None):
+        self.mk, self.dist = mk, dist
+        self.buckets = mk.buckets()
+        if not self.buckets:
+            raise RuntimeError("the context was not created with ext_sync=1")
+        self.q = queue if queue is not None else CudaFlagQueue(mk, dist, stream)
+        self.last_target = 0                             # highest flag value any queued wait is waiting for
+
+    @property
+    def stream(self):
+        return self.q.stream
+
+    @property
+    def grad(self):
+        return self.q.grad
+
     def enqueue(self, nsteps, first_step=None):
         """Queue the communication of a launch of `nsteps` steps. Call right AFTER mk.launch(nsteps)."""
-        torch, cu = self.torch, self.cu
         base = self.mk.steps_done if first_step is None else first_step
-        h = cu.CUstream(self.stream.cuda_stream)
-        geq = cu.CUstreamWaitValue_flags.CU_STREAM_WAIT_VALUE_GEQ
-        with torch.cuda.stream(self.stream):
-            for s, b in bucket_schedule(self.buckets, nsteps):
-                off, cnt = self.buckets[b]
-                self._check(cu.cuStreamWaitValue32(h, self.ready_ptr + 4 * b, base + s + 1, geq))
-                self.dist.all_reduce(self.grad[off:off + cnt])
-                self._check(cu.cuStreamWriteValue32(h, self.done_ptr + 4 * b, base + s + 1, 0))
+        for s, b in bucket_schedule(self.buckets, nsteps):
+            off, cnt = self.buckets[b]
+            self.q.wait_ready(b, base + s + 1)
+            self.q.all_reduce(off, cnt)
+            self.q.write_done(b, base + s + 1)
+        self.last_target = max(self.last_target, base + nsteps)
 
-    def finish(self):
-        self.stream.synchronize()
+    def cancel(self):
+        """Release every queued wait of this rank: its kernel will not raise the remaining ready flags (it stopped early), so
+        the host raises them to the last queued target. The collectives behind them then run on whatever the buckets hold; the
+        step they belong to is lost, which `wait()` reports on every rank."""
+        self.q.raise_ready(len(self.buckets), self.last_target)
+
+    def finish(self, timeout_s=120.0):
+        """Wait until the queue is empty. Returns False when it is not after `timeout_s` seconds (None = no limit)."""
+        return self.q.drain(timeout_s)
+
+    def wait(self, timeout_ms=600000, comm_timeout_s=120.0, kernel_wait=None):
+        """mk.wait + finish for a data-parallel launch, with the failure path: if this rank's kernel stopped early its queue is
+        cancelled first; then all ranks learn whether any of them failed and raise together (the failing rank its own error,
+        the others DataParallelAborted). `kernel_wait` replaces mk.wait in tests."""
+        err = None
+        try:
+            (kernel_wait or (lambda: self.mk.wait(timeout_ms)))()
+        except Exception as e:                           # OfaError from ofa_wait: device abort, timeout, CUDA error
+            err = e
+            self.cancel()
+        drained = self.finish(comm_timeout_s)
+        if not drained and err is None:
+            err = DataParallelAborted(f"the communication queue did not drain within {comm_timeout_s} s")
+        if drained:
+            any_failed = self.q.exchange_failed(err is not None)
+        else:
+            any_failed = True                            # this rank cannot take part in a collective any more
+        if err is not None:
+            raise err
+        if any_failed:
+            raise DataParallelAborted("another rank's kernel stopped early: the gradients of this launch are not valid")

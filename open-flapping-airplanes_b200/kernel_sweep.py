@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Standalone kernel sweep on one B200 (BASELINE config 5): every task kind of the megakernel run alone as a one-kind job on
+"""Standalone kernel sweep on one B200: every task kind of the megakernel run alone as a one-kind job on
 the persistent scheduler, at the GPT-S shapes, timed with CUDA events and reported against the measured roofline.
 
   python open-flapping-airplanes_b200/kernel_sweep.py [--only NAME[,NAME..]] [--repeats R] [--list]

@@ -16,12 +16,7 @@ sys.path.insert(0, ROOT)
 
 def log(msg):
     """progress lines (flushed) so that a run that is cut short still shows how far it got"""
-    path = os.environ.get("OFA_DP_LOG")
-    line = f"[rank {os.environ.get('RANK', '?')}] {msg}"
-    if path:
-        with open(f"{path}.rank{os.environ.get('RANK', '0')}.log", "a") as f:
-            f.write(line + "\n")
-    print(line, flush=True)
+    print(f"[rank {os.environ.get('RANK', '?')}] {msg}", flush=True)
 
 
 def main():
@@ -48,7 +43,7 @@ def main():
     dp = ofa.dp.DataParallel(mk, dist)
     log("communication stream warmed up")
     for n in (2, nsteps - 2):                      # two launches: the flags restart, the optimizer state continues
-        mk.launch(n); log(f"launched {n}"); dp.enqueue(n); log("enqueued"); mk.wait(60000); log("kernel done"); dp.finish(); log("comm done")
+        mk.launch(n); log(f"launched {n}"); dp.enqueue(n); log("enqueued"); dp.wait(60000, comm_timeout_s=60.0); log("kernel and communication done")
     losses = torch.tensor(mk.losses(), dtype=torch.float64, device="cuda")
     dist.all_reduce(losses); losses /= world
     w = torch.from_numpy(mk.read_weights()).cuda()

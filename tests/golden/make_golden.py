@@ -88,7 +88,7 @@ def main():
     probes = [0, 1, 50, 99, 100, 101, 2000, 3999, 4000]
     np.savez(os.path.join(HERE, "lr_schedule.npz"), steps=np.array(probes), lr=np.array([c.lr_at(s) for s in probes]),
              consts=np.array([c.LR_MAX, c.LR_MIN, c.WARMUP, c.STEPS, c.WD, c.BETAS[0], c.BETAS[1], c.SEED]))
-    # BASELINE config 1 dims (tied, because the reference's class is tied) with the constant lr of that config
+    # the tiny fp32 preset's dims (tied, because the reference's class is tied) with the constant lr of that config
     run_config(c, "tiny_tied", 65, 64, 2, 4, 64, 16, nsteps=3, ntok=1 << 14, constant_lr=3e-4)
     # an odd small shape, reference LR schedule
     run_config(c, "small_tied", 96, 32, 3, 2, 24, 3, nsteps=3, ntok=1 << 12)

@@ -77,3 +77,28 @@ def test_flat_layout_order(ofa, oracle):
     flat = ofa.flat_from_named({k: v.numpy() for k, v in w.items()}, cfg.L, tied=False)
     np.testing.assert_array_equal(flat, oracle.flatten(cfg, w))
     assert flat.size == 2 * 65 * 64 + 64 * 64 + 2 * (2 * 64 + 12 * 64 * 64) + 64
+
+
+def test_oversize_shared_memory_needs_are_refused_on_the_host(ofa):
+    """Tasks whose shared-memory need grows with the batch or the context are checked against the block's task area before
+    anything is built: a planning context (device < 0) is enough to see the refusal, nothing runs on a GPU."""
+    ok = ofa.default_config("gpt_s"); ok.device = -1
+    ofa.Megakernel(ok).close()
+    big = ofa.default_config("gpt_s"); big.device, big.batch = -1, 32                 # 32,768 tokens: the embedding-backward token list
+    with pytest.raises(ofa.OfaError) as e:
+        ofa.Megakernel(big)
+    assert e.value.code == ofa.capi.BAD_CONFIG and "embedding-backward" in str(e.value)
+    fwd = ofa.default_config("gpt_s"); fwd.device, fwd.batch, fwd.mode = -1, 32, ofa.capi.MODE_FORWARD
+    ofa.Megakernel(fwd).close()                                                        # no backward pass, no such task
+    dec = ofa.default_config("gpt_s"); dec.device, dec.ctx_len, dec.batch, dec.use_decode = -1, 2048, 2, 1
+    with pytest.raises(ofa.OfaError) as e:
+        ofa.Megakernel(dec)
+    assert e.value.code == ofa.capi.BAD_CONFIG and "serving tasks" in str(e.value)
+    dec.use_decode = 0
+    ofa.Megakernel(dec).close()                                                        # the same context without the serving job fits
+    # task level: refused before the device is looked at
+    K = ofa.capi
+    dims = dict(vocab=1024, d_model=768, n_layer=1, n_head=12, ctx_len=1024, batch=32)
+    with pytest.raises(ofa.OfaError) as e:
+        ofa.run_phases(K.DTYPE_BF16, dims, [ofa.phase(K.TK_EMB_WTE, [1 << 20, 1 << 21, 1 << 22])])
+    assert e.value.code == K.BAD_CONFIG

@@ -1,6 +1,6 @@
 """Model-level parity on the GPU through the C ABI (ofa_create / ofa_launch / ofa_wait / ofa_read_*): the whole training
 step and the live-weight decoder as ONE persistent launch, against the CPU oracle on the same seed and synthetic tokens.
-Bars (BASELINE north star): tiny fp32 model - loss/weights to fp32 rounding and greedy decode token-exact; bf16 model -
+Bars: tiny fp32 model - loss/weights to fp32 rounding and greedy decode token-exact; bf16 model -
 loss within 1e-2 relative, logits max-abs <= 2e-2, gradients per tensor L2 within 2 % / relmax 5e-2
 (llm/b200/megakernel/check_grads.py:14-21); runs are bitwise repeatable (llm/b200/megakernel/check_loss.sh)."""
 import numpy as np

@@ -65,7 +65,7 @@ def test_lr_schedule_matches_reference(oracle, golden_dir):
 
 
 def test_untied_head_changes_only_the_head(oracle):
-    """The untied variant (BASELINE configs) draws lm_head right after wpe and leaves every other tensor's recipe alone."""
+    """The untied variant (the GPT-S and tiny presets of this library) draws lm_head right after wpe and leaves every other tensor's recipe alone."""
     c_t = oracle.tiny_config(tied=True); c_u = oracle.tiny_config(tied=False)
     wt, wu = oracle.init_weights(c_t), oracle.init_weights(c_u)
     np.testing.assert_array_equal(wt["wte"].numpy(), wu["wte"].numpy())
