@@ -5,14 +5,16 @@ persistent megakernel, with the live-weight decoder running concurrently on its 
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload split|train_only]
 
-Timing: W warm-up steps run in a first persistent launch; the K timed steps are ONE further persistent launch bracketed
-by CUDA events on the launching stream (and a barrier + synchronize on both sides), max over ranks. `value` counts the
+Timing: W warm-up steps run in a first persistent launch; K timed steps are ONE further persistent launch bracketed by CUDA
+events on the launching stream (and a barrier + synchronize on both sides), max over ranks; that K-step launch is repeated
+(at least 5 times, more than a second in total) and the median launch is reported with the spread. `value` counts the
 tokens all ranks trained on. The working set of a step (326 MB of bf16 weights + GBs of activations) exceeds the 126 MB L2,
 so no explicit flush is needed. `e2e` repeats the K steps through the public API with host buffers: token upload, launch,
 wait and loss read-back inside a host-timed region.
 
---impl reference: the CPU implementation of the same step (the oracle port of the reference's PyTorch model) on all host
-cores, on a bounded sample (whole sequences of the same batch).
+--impl reference: the CPU implementation of the same step (the oracle port of the reference's PyTorch model, batch 4 x 1024,
+forward + backward + AdamW) on all host cores; it runs as many of the requested steps as fit in about two minutes and prints
+how many it ran.
 """
 import argparse
 import importlib
@@ -32,8 +34,9 @@ V, D, L, H, T, B = 50304, 768, 12, 12, 1024, 4
 TOKENS_PER_STEP = B * T
 P_MM = L * 12 * D * D + V * D                                   # matmul parameters
 FLOP_PER_STEP = 6 * TOKENS_PER_STEP * P_MM + L * 3.5 * (4 * B * H * T * T * (D // H) / 2)   # 3.307e12, causal attention counted once
-# dram__bytes_read.sum + dram__bytes_write.sum of the megakernel per step, split workload on one GPU (ncu capture of a 2-step launch,
-# concurrent decoder included; the profiles folder holds the command and the raw figures)
+# dram__bytes_read.sum + dram__bytes_write.sum of the megakernel per step, split workload on one GPU: a constant taken from ONE ncu
+# capture of a 2-step launch (concurrent decoder included), not measured by this program. profiles/ofa_kernel_bench_split_dram_traffic.md
+# holds the command, the raw figures, the date and the commit of the capture; it has to be re-captured when the training graph changes.
 SPLIT_DRAM_BYTES_PER_STEP = 19.3e9
 
 
@@ -103,8 +106,11 @@ def init_flat(mk, seed=1234):
     return flat
 
 
-def cpu_step_tokens_per_s(max_seconds=30.0):
-    """The oracle's training step (fp32, all host threads) on whole sequences of the GPT-S batch; returns (tok/s, cores, sample)."""
+def cpu_steps(warmup, steps, max_seconds):
+    """The oracle's training step - the reference's PyTorch model and recipe, fp32, all host threads - on the SAME step the GPU arm
+    runs: batch 4 x 1024 tokens of the same synthetic stream, forward + backward + one AdamW update of the full 163M-parameter
+    model per step. Runs `warmup` untimed and up to `steps` timed steps, stopping early when `max_seconds` of timed work are used
+    up. Returns (tokens/s, cores, warm-ups run, steps timed, seconds per step list)."""
     import torch
     from oracle import gpt_oracle as orc
     cores = os.cpu_count() or 1
@@ -113,32 +119,41 @@ def cpu_step_tokens_per_s(max_seconds=30.0):
     w0 = orc.init_weights(cfg)
     model = orc.GPTOracle(cfg, w0, "fp32")
     opt = orc.make_optimizer(cfg, model)
-    tokens = orc.synthetic_tokens(V, 1 << 16, 0)
-    nseq, t_total, ntok = 0, 0.0, 0
-    # first sequence warms the allocator and is not counted; then as many sequences as fit in the time budget (at least one,
-    # at most 12 steps' worth)
-    for i in range(1 + 12 * B):
-        seq = tokens[i * 1100:i * 1100 + T + 1].astype(np.int64)
-        x = torch.from_numpy(seq[None, :-1]).contiguous(); y = torch.from_numpy(seq[None, 1:]).contiguous()
+    ntok = 1 << 20
+    tokens = orc.synthetic_tokens(V, ntok, 1000)
+    starts = orc.batch_starts(cfg, ntok, warmup + steps)
+    def one(i):
+        for g in opt.param_groups:
+            g["lr"] = orc.lr_at(cfg, i)
+        x, y = orc.get_batch(cfg, tokens, starts[i])
         t0 = time.perf_counter()
         loss = model(x, y); loss.backward(); opt.step(); opt.zero_grad(set_to_none=True)
-        dt = time.perf_counter() - t0
-        if i == 0 and dt < max_seconds / 3:
-            continue
-        nseq += 1; t_total += dt; ntok += T
-        if t_total + dt > max_seconds:
+        return time.perf_counter() - t0
+
+    times, w_done, i = [], 0, 0
+    for _ in range(warmup):
+        dt = one(i); i += 1; w_done += 1
+        if dt > max_seconds / 3:                       # a host this slow gets one warm-up only
             break
-    return ntok / t_total, cores, f"{nseq} sequence(s) of {T} tokens, fp32 forward+backward+AdamW of the full 163M-parameter model, {t_total:.1f} s"
+    for _ in range(steps):
+        dt = one(i); i += 1
+        times.append(dt)
+        if sum(times) + dt > max_seconds:
+            break
+    total = sum(times)
+    return TOKENS_PER_STEP * len(times) / total, cores, w_done, len(times), times
 
 
 def run_reference(args, rank, world):
     if rank != 0:
         return
-    tps, cores, sample = cpu_step_tokens_per_s(max_seconds=25.0 * max(1, min(args.steps, 3)))
-    line = {"impl": "reference", "metric": "GPT-S 162M train tokens/s", "value": tps, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": TOKENS_PER_STEP / tps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+    tps, cores, w_done, k_done, times = cpu_steps(max(1, min(args.warmup, 2)), max(1, args.steps), max_seconds=120.0)
+    sample = (f"{k_done} timed step(s) after {w_done} warm-up step(s), each the full step: batch {B} x {T} tokens, fp32 forward + backward + AdamW of the "
+              f"163M-parameter model; {sum(times):.1f} s of timed work")
+    line = {"impl": "reference", "metric": "GPT-S 162M train tokens/s", "value": tps, "unit": "tokens/s", "n_gpus": args.gpus, "steps": k_done,
+            "warmup": w_done, "steps_requested": args.steps, "ms_per_step": TOKENS_PER_STEP / tps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "gpt_s V=50304 untied D=768 L=12 H=12 T=1024 B=4, CPU oracle port of the reference PyTorch model"},
+            "config": {"workload": "gpt_s V=50304 untied D=768 L=12 H=12 T=1024 B=4 (4096 tok/step), CPU oracle port of the reference PyTorch model, training only"},
             "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
@@ -150,8 +165,10 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="split", choices=["split", "train_only"])
+    ap.add_argument("--workload", default="split", choices=["split", "train_only", "ref_split", "ref_train_only"],
+                    help="ref_*: the same two workloads at the shapes the reference program is compiled for (vocab 100352 tied, context 512, batch 8), for a like-for-like line beside its own binary")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--repeats", type=int, default=0, help="timed K-step launches (0 = enough for more than a second of timed work, at least 5)")
     ap.add_argument("--phase-table", action="store_true", help="also print the per-phase busy table to stderr")
     ap.add_argument("--cfg", action="append", default=[], metavar="FIELD=INT", help="override an integer field of ofa_config (experiments, e.g. gemm_nsub=2, attn_legacy=1); the run is then not the headline configuration")
     args = ap.parse_args()
@@ -171,9 +188,17 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     W, K = max(3, args.warmup), args.steps
-    split = args.workload == "split"
+    split = args.workload in ("split", "ref_split")
+    ref_shapes = args.workload.startswith("ref_")
+    global V, T, B, TOKENS_PER_STEP, FLOP_PER_STEP
+    if ref_shapes:                                      # llm/b200/megakernel/ofa.cu:71
+        V, T, B = 100352, 512, 8
+        TOKENS_PER_STEP = B * T
+        FLOP_PER_STEP = 6 * TOKENS_PER_STEP * (L * 12 * D * D + V * D) + L * 3.5 * (4 * B * H * T * T * (D // H) / 2)
 
     cfg = ofa.default_config("gpt_s")
+    if ref_shapes:
+        cfg.vocab, cfg.valid_vocab, cfg.tied_head, cfg.ctx_len, cfg.batch = V, 100277, 1, T, B
     cfg.device = local_rank
     cfg.data_seed = rank
     if split:
@@ -181,7 +206,7 @@ def main():
         cfg.use_decode = 1 if rank == 0 else 0
         if rank != 0:
             cfg.reserved_sms = 32                      # other ranks leave the serving partition idle so that all ranks train on 116 SMs
-        prompt = np.random.default_rng(1234).integers(0, V, size=6)
+        prompt = np.random.default_rng(1234).integers(0, min(V, 100277), size=6)
         for i, t in enumerate(prompt):
             cfg.prompt[i] = int(t)
         cfg.n_prompt, cfg.answer_len, cfg.temperature = 6, 256, 0.0
@@ -221,17 +246,26 @@ def main():
 
     run(W)
     barrier()
+    # The K-step launch is repeated so that the timed work exceeds a second (one launch of 20 steps is 0.18 s: too few clock samples
+    # and no spread); every launch is K steps bracketed by its own CUDA events, the reported time is the median launch.
+    est = run(K)
+    barrier()
+    reps = int(min(25, max(5, np.ceil(1200.0 / max(est, 1e-3))))) if args.repeats <= 0 else args.repeats
     dec0 = mk.decode_steps
     sampler = ClockSampler(local_rank); sampler.start()
     time.sleep(0.25)
-    ms = run(K)
-    barrier()
+    all_ms = []
+    for _ in range(reps):
+        m = run(K)
+        barrier()
+        if dist is not None:
+            t = torch.tensor([m], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            m = float(t.item())
+        all_ms.append(m)
     clocks = sampler.stop()
     dec_steps = mk.decode_steps - dec0
-    if dist is not None:
-        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+    ms = float(np.median(all_ms))
     losses = mk.losses()
 
     # ---- end to end through the public API with host buffers (rank-local; inputs uploaded and results read inside the timed region)
@@ -258,19 +292,20 @@ def main():
         achieved_tf = FLOP_PER_STEP * K / (ms * 1e-3) / 1e12
         value = world * TOKENS_PER_STEP * K / (ms * 1e-3)
         # sampled decode tokens: of every 261 decode steps (5 forced + 256 sampled) 256 are counted, as the reference counts (ofa.cu:747-752)
-        dec_tok_s = (dec_steps * 256.0 / 261.0) / (ms * 1e-3) if split else None
+        dec_tok_s = (dec_steps * 256.0 / 261.0) / (sum(all_ms) * 1e-3) if split else None
         line = {
             "metric": "GPT-S 162M train tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": ("gpt_s V=50304 untied D=768 L=12 H=12 T=1024 B=4 (4096 tok/step/GPU), " +
+            "ms_per_step": ms / K, "timed_launches": {"n": reps, "steps_each": K, "ms_per_step_median": ms / K, "ms_per_step_min": min(all_ms) / K, "ms_per_step_max": max(all_ms) / K},
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": ((f"gpt_s at the reference program's shapes V={V} tied D=768 L=12 H=12 T={T} B={B} (4096 tok/step/GPU), " if ref_shapes else "gpt_s V=50304 untied D=768 L=12 H=12 T=1024 B=4 (4096 tok/step/GPU), ") +
                                     ("116 train / 24 serve / 8 reserved SMs with concurrent batch-1 greedy decode (6-token prompt, 256 generated, repeating)" if split else "training only on all SMs")),
-                       "parallelism": f"dp{world}", "l2": "working set per step (>2 GB) exceeds the 126 MB L2; no flush needed",
+                       "parallelism": f"dp{world}" + (", ranks > 0 train on 116 SMs and leave the 24 serving SMs idle (one serving replica, on rank 0)" if (world > 1 and split) else ""), "l2": "working set per step (>2 GB) exceeds the 126 MB L2; no flush needed",
                        "projected_4000_steps_s": ms / K * 4000 / 1e3, **({"overrides": args.cfg} if args.cfg else {})},
             "decode_tok_s": dec_tok_s, "final_loss": float(losses[-1]), "first_loss": float(losses[0]),
             "e2e": {"value": world * TOKENS_PER_STEP * K / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": int(window.nbytes / K + starts.nbytes / K), "d2h_bytes_per_step": 4},
             "gpu_launches": 1,
             "roofline": {"bound": "tensor", "achieved": achieved_tf, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved_tf / peak_tf,
-                         "traffic": SPLIT_DRAM_BYTES_PER_STEP if (args.workload == "split" and world == 1) else None, "peak_source": f"{how} bf16_tflops_sustained x {sms_used}/148 SMs", "flop_per_step": FLOP_PER_STEP},
+                         "traffic": SPLIT_DRAM_BYTES_PER_STEP if (args.workload == "split" and world == 1 and not args.cfg) else None, "peak_source": f"{how} bf16_tflops_sustained x {sms_used}/148 SMs", "flop_per_step": FLOP_PER_STEP},
             "clocks": clocks,
         }
         if args.phase_table:
@@ -299,9 +334,10 @@ def main():
                     print(f"    {n:22s} {(a - t0) / 1e6:8.3f} -> {(b - t0) / 1e6:8.3f}  ({(b - a) / 1e3:7.1f} us)", file=sys.stderr)
             for p in sorted(mk.phases(), key=lambda p: -p["busy_ns"])[:40]:
                 print(f"  {p['name']:24s} tasks {p['ntasks']:6d}  busy {p['busy_ns'] / 1e6 / K:8.3f} ms/step  {100.0 * p['busy_ns'] / tot:5.1f} %", file=sys.stderr)
-        if world == 1 and not args.no_cpu_baseline:
-            tps, cores, sample = cpu_step_tokens_per_s(max_seconds=20.0)
-            line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}
+        if world == 1 and not args.no_cpu_baseline and not ref_shapes:
+            tps, cores, w_done, k_done, times = cpu_steps(1, 3, max_seconds=25.0)
+            line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port",
+                                    "sample": f"{k_done} timed step(s) after {w_done} warm-up, each the full step (batch {B} x {T} tokens, fp32 forward + backward + AdamW, training only), {sum(times):.1f} s"}
         print(json.dumps(line), flush=True)
     mk.close()
     if dist is not None:

@@ -65,7 +65,7 @@ typedef struct {
   int adam_interleave;      /* experimental, default 0: 1 = each layer's AdamW phase inside the backward pass; n >= 2 = AdamW trickles through the backward pass, up to n tasks after every backward phase */
   int head_dx_splitk;       /* 1: compute lm_head dX as K-split partial products + reduce (experimental, default 0)     */
   int gemm_nsub;            /* consecutive 128-wide N tiles per GEMM task (0 = default)                           */
-  double timeout_s;         /* device-side bound for any dependency wait (0 = default 20 s)                       */
+  double timeout_s;         /* device-side bound for a wait on an external flag (0 = default 20 s); waits for dependencies inside the graph give up after 1.5 x this */
   int device;               /* CUDA device ordinal; < 0 = planning context: layout, buckets and phase graphs are built and can be queried, nothing touches a device and nothing can be launched */
 } ofa_config;
 

@@ -164,6 +164,9 @@ __device__ __forceinline__ void run_decode_task(const Ctx& C, const PhaseDesc& d
 __device__ __forceinline__ int wait_deps(const Ctx& C, const Job& J, int job_id, int step, int ph, int local, const volatile int* rec) {
   const int cnt = rec[2];
   const u64 t0 = gtimer();
+  // a dependency may legitimately sit behind an external wait that is about to give up: its own bound is half as long again, so
+  // that the status names the external flag that was never raised and not one of the tasks queued behind it
+  const u64 limit = C.dep_timeout_ns + (C.dep_timeout_ns >> 1);
   unsigned spins = 0;
   if (cnt >= 0) {
     // up to four dependencies from the phase's scheduling record: their counters are read with relaxed loads that are all in
@@ -185,7 +188,7 @@ __device__ __forceinline__ int wait_deps(const Ctx& C, const Job& J, int job_id,
       if (job_id == 1 && C.use_train && ld_relaxed(C.finished)) return -2;
       if ((++spins & 63u) == 0) {
         if (aborted(C.status)) return -2;
-        if (gtimer() - t0 > C.dep_timeout_ns) { raise_abort(C.status, ST_DEP_TIMEOUT, ph, local, step); return -2; }
+        if (gtimer() - t0 > limit) { raise_abort(C.status, ST_DEP_TIMEOUT, ph, local, step); return -2; }
       }
       __nanosleep(job_id == 1 ? 20 : 80);
     }
@@ -202,7 +205,7 @@ __device__ __forceinline__ int wait_deps(const Ctx& C, const Job& J, int job_id,
     if (job_id == 1 && C.use_train && ld_relaxed(C.finished)) return -2;
     if ((++spins & 63u) == 0) {
       if (aborted(C.status)) return -2;
-      if (gtimer() - t0 > C.dep_timeout_ns) { raise_abort(C.status, ST_DEP_TIMEOUT, ph, local, step); return -2; }
+      if (gtimer() - t0 > limit) { raise_abort(C.status, ST_DEP_TIMEOUT, ph, local, step); return -2; }
     }
     __nanosleep(job_id == 1 ? 20 : 80);
   }

@@ -676,6 +676,8 @@ bool build_decode_graph(ofa_ctx* c) {
   c->d_scal = c->ar.alloc<int>(8); st.scal = c->d_scal;
   st.kv = c->ar.alloc<T>((size_t)L * 2 * m.H * m.T * m.DH);
   st.logits = c->ar.alloc<float>(m.V);
+  c->bufs["dec_kv"] = std::make_pair((void*)st.kv, (size_t)L * 2 * m.H * m.T * m.DH * sizeof(T));   // [L][2][H][T][DH], for parity checks
+  c->bufs["dec_scal"] = std::make_pair((void*)c->d_scal, sizeof(int) * 8);                               // token, pos, step, ctx_full, astep, poskey, epoch
   c->out_cap = cfg.decode_out_cap > 0 ? cfg.decode_out_cap : 65536;
   if (c->ar.dry) { c->d_out = c->ar.alloc<int>(c->out_cap); }
   else {

@@ -33,7 +33,7 @@ GEMMS = {
     "gemm_dln1": (1, 0, M, D, 3 * D), "gemm_head_dX": (0, 0, M, D, V), "gemm_dWqkv": (2, 4, D, 3 * D, M), "gemm_dWo": (2, 4, D, D, M),
     "gemm_dWup": (2, 4, D, FF, M), "gemm_dWdown": (2, 4, FF, D, M), "gemm_head_dW": (2, 4, V, D, M),
 }
-OTHERS = ["attn_fwd", "attn_bwd", "adamw", "cross_entropy", "ln_fwd", "ln_bwd", "embed_bwd_wte", "decode_148sm", "decode_24sm"]
+OTHERS = ["attn_fwd", "attn_bwd", "adamw", "cross_entropy", "ln_fwd", "ln_bwd", "embed_bwd_wte", "decode_148sm", "decode_24sm", "decode_attn"]
 
 
 def peaks():
@@ -56,6 +56,8 @@ def run_gemm(ofa, name, repeats, nsub):
     out_b = 4 if epi == 4 else 2
     bytes_set = 2 * (Mm * Kk + Kk * Nn) + out_b * Mm * Nn + (2 * Mm * Nn if epi in (1, 2, 3) else 0)
     nsets = max(1, min(16, -(-2 * L2_BYTES // bytes_set)))
+    if REF_METHOD:
+        nsets = 1
     keep, phases = [], []
     for _ in range(nsets):
         A = rand_bf16(ofa, rng, ashape); Bm = rand_bf16(ofa, rng, bshape)
@@ -63,11 +65,18 @@ def run_gemm(ofa, name, repeats, nsub):
         aux = rand_bf16(ofa, rng, (Mm, Nn), 1.0) if epi in (1, 3) else (ofa.DeviceBuffer((Mm, Nn), "bf16") if epi == 2 else None)
         keep += [A, Bm, C, aux]
         phases.append(ofa.gemm_phase(layout, epi, Mm, Nn, Kk, A, ashape[1], Bm, bshape[1], C, Nn, aux, Nn if aux is not None else 0, nsub=nsub))
-    ms = ofa.run_phases(K.DTYPE_BF16, DIMS, phases, repeats=repeats) / (repeats * nsets)
     flop = 2.0 * Mm * Nn * Kk
-    return {"kernel": name, "shape": [Mm, Nn, Kk], "ms": ms, "tflops": flop / ms / 1e9, "bound": "tensor", "algorithmic_bytes": bytes_set, "buffer_sets": nsets}
+    if REF_METHOD:      # the reference test's method (llm/gemm/test_gemm.cu:179-190,284): same operands, 20 (5 for the largest) back-to-back passes, best of 6
+        it = 5 if flop > 5e11 else 20
+        ofa.run_phases(K.DTYPE_BF16, DIMS, phases, repeats=2)
+        ms = min(ofa.run_phases(K.DTYPE_BF16, DIMS, phases, repeats=it) / it for _ in range(6))
+    else:
+        ms = ofa.run_phases(K.DTYPE_BF16, DIMS, phases, repeats=repeats) / (repeats * nsets)
+    return {"kernel": name, "shape": [Mm, Nn, Kk], "ms": ms, "tflops": flop / ms / 1e9, "bound": "tensor", "algorithmic_bytes": bytes_set, "buffer_sets": nsets,
+            "timing": "same operands, best of 6 x back-to-back passes in one launch" if REF_METHOD else "operands rotated beyond L2"}
 
 
+REF_METHOD = False   # --ref-method: time GEMMs the way the reference's test program does (warm operands, best of several)
 ATTN_LEGACY = 0      # --attn-legacy: time the mma.sync attention tasks instead of the tcgen05 ones
 
 
@@ -182,6 +191,34 @@ def run_decode(ofa, sms, ntok):
     return {"kernel": f"decode_{sms}sm", "shape": [sms], "ms": ms / ntok, "tok_s": ntok / ms * 1e3, "gbs": by / (ms / ntok) / 1e6, "bound": "hbm", "algorithmic_bytes": by}
 
 
+def run_decode_attn(ofa, sms=148):
+    """The serving job's attention task (one head's softmax attention over the KV cache + its slice of Wo; the reference's task_attwo,
+    llm/b200/megakernel/decode_wide.cuh:321-428) at KV lengths 128 ... 1024: a decode-only context walks one context from position 0
+    to 1023 in launches of 128 tokens, and after each launch the summed task time of the 12 "att+wo" phases gives the mean time of
+    one task at the KV lengths of that window. Bytes per task: K and V rows of one head up to the position (2 * len * 64 * 2 B)
+    plus the task's Wo slice (64 x 256 x 2 B). Returns one record per window."""
+    cfg = ofa.default_config("gpt_s")
+    cfg.mode, cfg.use_decode, cfg.infer_sms, cfg.reserved_sms = ofa.capi.MODE_DECODE_ONLY, 1, sms, 0
+    cfg.n_prompt, cfg.answer_len = 1, 0                      # no answer mode: the context simply grows to 1024 positions
+    cfg.prompt[0] = 11
+    mk = ofa.Megakernel(cfg)
+    rng = np.random.default_rng(6)
+    mk.load_weights(rng.standard_normal(mk.num_params, dtype=np.float32) * np.float32(0.02))
+    out = []
+    for w in range(T // 128):
+        ms = mk.run(128)
+        ph = [p for p in mk.decode_phases() if p["name"].endswith("att+wo")]
+        ntasks = sum(p["ntasks"] for p in ph) * 128
+        us = sum(p["busy_ns"] for p in ph) / 1e3 / ntasks
+        mean_len = w * 128 + 64.5
+        by = 2.0 * mean_len * 64 * 2 + 64 * 256 * 2
+        out.append({"kernel": f"decode_attn_kv{(w + 1) * 128}", "shape": [int(w * 128 + 1), int((w + 1) * 128)], "us_per_task": us, "ms": us / 1e3,
+                    "tok_s": 128 / ms * 1e3, "gbs_per_block": by / us / 1e3, "gbs": by / us / 1e3 * 2 * sms, "bound": "hbm", "algorithmic_bytes": by,
+                    "note": "gbs = per-task rate x the 2 x %d resident serving blocks (the rate if every block ran such tasks back to back)" % sms})
+    mk.close()
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default="")
@@ -189,9 +226,15 @@ def main():
     ap.add_argument("--nsub", type=int, default=0)
     ap.add_argument("--attn-legacy", action="store_true")
     ap.add_argument("--list", action="store_true")
+    ap.add_argument("--ref-method", action="store_true", help="GEMM cases: the reference test program's timing method (same operands repeated, best of 6)")
+    ap.add_argument("--ref-vocab", action="store_true", help="GEMM cases with a vocabulary dimension use the reference's 100352 instead of 50304")
     a = ap.parse_args()
-    global ATTN_LEGACY
+    global ATTN_LEGACY, REF_METHOD
     ATTN_LEGACY = 1 if a.attn_legacy else 0
+    REF_METHOD = a.ref_method
+    if a.ref_vocab:
+        for k, (l, e, m, n, kk) in list(GEMMS.items()):
+            GEMMS[k] = (l, e, 100352 if m == V else m, 100352 if n == V else n, 100352 if kk == V else kk)
     names = list(GEMMS) + OTHERS
     if a.list:
         print("\n".join(names)); return
@@ -213,10 +256,12 @@ def main():
         elif n == "embed_bwd_wte": r = run_embed_bwd(ofa, a.repeats)
         elif n == "decode_148sm": r = run_decode(ofa, 148, 261 * max(1, a.repeats))
         elif n == "decode_24sm": r = run_decode(ofa, 24, 261 * max(1, a.repeats))
+        elif n == "decode_attn": r = run_decode_attn(ofa)
         else: raise SystemExit(f"unknown case {n}")
-        r["frac"] = (r["tflops"] / tf) if r["bound"] == "tensor" else (r["gbs"] / hbm)
-        r["peak"] = f"{how}: {tf if r['bound'] == 'tensor' else hbm} {'TFLOP/s (burst)' if r['bound'] == 'tensor' else 'GB/s'}"
-        print(json.dumps(r), flush=True)
+        for rec in (r if isinstance(r, list) else [r]):
+            rec["frac"] = (rec["tflops"] / tf) if rec["bound"] == "tensor" else (rec["gbs"] / hbm)
+            rec["peak"] = f"{how}: {tf if rec['bound'] == 'tensor' else hbm} {'TFLOP/s (burst)' if rec['bound'] == 'tensor' else 'GB/s'}"
+            print(json.dumps(rec), flush=True)
 
 
 if __name__ == "__main__":

@@ -1,0 +1,186 @@
+"""Parity of the bf16 live-weight decoder (the <bf16, 768, 64> serving job) on the GPU, through the C ABI, the two ways the
+reference checks its decoder:
+  * logits of every decode step against ONE full-sequence fp32 forward over the tokens that were fed, rel <= 3e-2 per step and
+    >= 99 % argmax agreement (llm/decode/ref_decode.py:45-78), plus the key / value cache against the same forward;
+  * tokens, final logits and the whole KV cache bit-identical across schedules: serving partitions of different sizes and
+    permuted task orders (llm/decode/test_decode.cu:135-158).
+Also covered: the context-overflow restart, launches that stop in the middle of a token and resume, and decoding while the
+training job runs in the same launch (frozen weights, so the tokens must equal a decode-only run's)."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def relmax(a, b):
+    a, b = np.asarray(a, dtype=np.float64), np.asarray(b, dtype=np.float64)
+    return np.abs(a - b).max() / max(np.abs(b).max(), 1e-30)
+
+
+def make_ctx(ofa, oracle, w, ocfg, prompt, infer_sms=0, answer_len=0, temperature=0.0, mode=None, seed=0xC0FFEE):
+    cfg = ofa.default_config("gpt_s")
+    cfg.vocab, cfg.valid_vocab, cfg.n_layer, cfg.ctx_len, cfg.batch = ocfg.V, ocfg.V - 3, ocfg.L, ocfg.T, ocfg.B
+    cfg.mode = ofa.capi.MODE_DECODE_ONLY if mode is None else mode
+    cfg.use_decode, cfg.infer_sms, cfg.n_prompt, cfg.answer_len, cfg.temperature, cfg.decode_seed = 1, infer_sms, len(prompt), answer_len, temperature, seed
+    cfg.decode_out_cap = 65536
+    for i, t in enumerate(prompt):
+        cfg.prompt[i] = int(t)
+    mk = ofa.Megakernel(cfg)
+    mk.load_weights(oracle.flatten(ocfg, w))
+    return mk
+
+
+def read_kv(mk, ocfg):
+    return mk.read_buffer("dec_kv", (ocfg.L, 2, ocfg.H, ocfg.T, ocfg.DH), "bf16")
+
+
+def fed_tokens(prompt, ring, n):
+    """tokens the decoder consumed at steps 0..n-1 when it starts from `prompt` without answer mode: the prompt, then its samples"""
+    fed = list(prompt)
+    for i in range(len(prompt) - 1, n - 1):
+        fed.append(int(ring[i]))
+    return fed[:n]
+
+
+@pytest.mark.parametrize("shape", ["small", "gpt_s"])
+def test_bf16_decode_logits_and_kv_match_full_sequence_forward(ofa, oracle, shape):
+    if shape == "small":
+        ocfg = oracle.OracleConfig(V=1024, D=768, L=2, H=12, T=256, B=1, tied=False)
+    else:
+        ocfg = oracle.gpt_s_config(); ocfg.B = 4
+    w = oracle.decode_test_weights(ocfg)
+    rng = np.random.default_rng(5)
+    prompt = [int(t) for t in rng.integers(0, ocfg.V - 3, size=8)]
+    nsteps = 64
+    mk = make_ctx(ofa, oracle, w, ocfg, prompt)
+    logits = np.empty((nsteps, ocfg.V), dtype=np.float32)
+    for i in range(nsteps):                      # one token per launch: every launch resumes the context of the one before
+        mk.run(1, timeout_ms=60000)
+        logits[i] = mk.decode_logits()
+    assert mk.decode_steps == nsteps
+    ring = mk.decode_tokens(nsteps)
+    toks = fed_tokens(prompt, ring, nsteps)
+    ref, kv_ref = oracle.forward_with_kv(ocfg, w, toks)
+    ref = ref.numpy()
+    rel = np.abs(logits - ref).max(1) / np.abs(ref).max(1)
+    vv = ocfg.V - 3
+    agree = float((logits[:, :vv].argmax(1) == ref[:, :vv].argmax(1)).mean())
+    assert rel.max() <= 3e-2, rel.max()
+    assert agree >= 0.99, agree
+    # sampled tokens are the argmax over the valid vocabulary of the logits the step produced (ties to the lower id)
+    for i in range(len(prompt) - 1, nsteps):
+        assert int(ring[i]) == int(logits[i, :vv].argmax())
+    kv = read_kv(mk, ocfg)[:, :, :, :nsteps, :]
+    assert relmax(kv, kv_ref.numpy()) <= 2e-2
+    mk.close()
+
+
+def _run_schedule(ofa, oracle, w, ocfg, prompt, nsteps, infer_sms, shuffle, chunks=(None,)):
+    lib = ofa.capi.load()
+    lib.ofa_debug_set_task_shuffle(shuffle)
+    try:
+        mk = make_ctx(ofa, oracle, w, ocfg, prompt, infer_sms=infer_sms, temperature=0.9)
+        done = 0
+        for c in chunks:
+            n = nsteps - done if c is None else c
+            mk.run(n, timeout_ms=120000); done += n
+        out = (mk.decode_tokens(nsteps).copy(), mk.decode_logits().copy(), mk.read_buffer("dec_kv", (ocfg.L, 2, ocfg.H, ocfg.T, ocfg.DH), np.uint16).copy())
+        mk.close()
+        return out
+    finally:
+        lib.ofa_debug_set_task_shuffle(0)
+
+
+def test_bf16_decode_is_bitwise_independent_of_the_schedule(ofa, oracle):
+    """8 prompt tokens, then free-running sampling at temperature 0.9 (96 steps), as test_decode.cu:139-141: the serving job on all
+    SMs, on 24, on 5 and on ONE SM (two blocks), in natural and permuted task order, and cut into several launches, must give the
+    same tokens, the same final logits and the same KV cache to the bit."""
+    ocfg = oracle.OracleConfig(V=1024, D=768, L=2, H=12, T=256, B=1, tied=False)
+    w = oracle.decode_test_weights(ocfg)
+    prompt = [int(t) for t in np.random.default_rng(6).integers(0, ocfg.V - 3, size=8)]
+    NS = 96
+    base = _run_schedule(ofa, oracle, w, ocfg, prompt, NS, 0, 0)
+    assert len(set(int(t) for t in base[0][8:])) > 8               # sampling produced a non-trivial stream
+    for name, sms, shuffle, chunks in [("24 SMs", 24, 0, (None,)), ("all SMs permuted", 0, 12345, (None,)), ("5 SMs permuted", 5, 777, (None,)),
+                                       ("1 SM", 1, 0, (None,)), ("24 SMs, three launches", 24, 99, (17, 40, None))]:
+        got = _run_schedule(ofa, oracle, w, ocfg, prompt, NS, sms, shuffle, chunks)
+        assert np.array_equal(got[0], base[0]), name + ": tokens"
+        assert np.array_equal(got[1].view(np.uint32), base[1].view(np.uint32)), name + ": final logits"
+        assert np.array_equal(got[2], base[2]), name + ": KV cache"
+    other = make_ctx(ofa, oracle, w, ocfg, prompt, temperature=0.9, seed=1)
+    other.run(NS, timeout_ms=120000)
+    assert not np.array_equal(other.decode_tokens(NS), base[0])     # a different seed gives a different stream
+    other.close()
+
+
+def test_bf16_decode_restarts_when_the_context_is_full(ofa, oracle):
+    """Context of 128 positions, 150 steps without answer mode: after position 127 the decoder starts a new context at position 0
+    with the token it just sampled (llm/b200/megakernel/decode_wide.cuh:619-620). The logits of the last step must match a
+    full-sequence forward over the tokens fed since the restart."""
+    ocfg = oracle.OracleConfig(V=1024, D=768, L=2, H=12, T=128, B=1, tied=False)
+    w = oracle.decode_test_weights(ocfg)
+    prompt = [int(t) for t in np.random.default_rng(7).integers(0, ocfg.V - 3, size=4)]
+    n = 150
+    mk = make_ctx(ofa, oracle, w, ocfg, prompt)
+    mk.run(n, timeout_ms=120000)
+    ring = mk.decode_tokens(n)
+    fed = fed_tokens(prompt, ring, n)
+    scal = mk.read_buffer("dec_scal", (8,), np.int32)
+    assert scal[2] == n and scal[1] == n - 128                     # steps taken; position inside the second context
+    ref, _ = oracle.forward_with_kv(ocfg, w, fed[128:n])
+    assert relmax(mk.decode_logits(), ref[-1].numpy()) <= 3e-2
+    mk.close()
+
+
+def test_decode_beside_training_equals_decode_only_with_frozen_weights(ofa, oracle):
+    """Training (forward + backward, no optimizer: the weights stay frozen) and the serving job in ONE launch on a 116/24/8 split,
+    over three launches that each cut the decoder off in the middle of a token: the tokens it produced must be exactly the
+    prefix of a decode-only run from the same weights, and training must still produce its losses."""
+    ocfg = oracle.OracleConfig(V=1024, D=768, L=2, H=12, T=256, B=2, tied=False)
+    w = oracle.decode_test_weights(ocfg)
+    prompt = [int(t) for t in np.random.default_rng(8).integers(0, ocfg.V - 3, size=6)]
+    cfg_mode = ofa.capi.MODE_NO_OPT
+    mk = make_ctx(ofa, oracle, w, ocfg, prompt, infer_sms=24, answer_len=40, mode=cfg_mode)
+    tokens = oracle.synthetic_tokens(ocfg.V, 1 << 15, 0)
+    mk.set_tokens(tokens)
+    total = 0
+    for nsteps in (30, 30, 30):
+        mk.run(nsteps, timeout_ms=120000)
+        total = mk.decode_steps
+    assert total >= 20, total                                       # the decoder made progress beside the trainer
+    total = min(total, 4000)
+    got = mk.decode_tokens(total)
+    losses = mk.losses()
+    assert np.all(np.isfinite(losses)) and len(losses) == 90
+    mk.close()
+    ref = make_ctx(ofa, oracle, w, ocfg, prompt, infer_sms=24, answer_len=40)
+    ref.run(total, timeout_ms=120000)
+    want = ref.decode_tokens(total)
+    np.testing.assert_array_equal(got, want)
+    assert want[0] == ofa.capi.OUT_RESTART and all(t == ofa.capi.OUT_FORCED for t in want[1:5])
+    ref.close()
+
+
+def test_tiny_fp32_decode_resumes_exactly_across_launches_beside_training(ofa, oracle):
+    """The fp32 preset: forward-only training job + decoder in one launch, several launches; the greedy tokens must equal the CPU
+    oracle's greedy decode from the same (unchanged) weights, token for token."""
+    ocfg = oracle.tiny_config(tied=False)
+    w0 = oracle.init_weights(ocfg)
+    prompt = [int(t) for t in np.random.default_rng(0).integers(0, 65, size=8)]
+    cfg = ofa.default_config("tiny")
+    cfg.mode, cfg.use_decode, cfg.infer_sms, cfg.answer_len = ofa.capi.MODE_FORWARD, 1, 16, 0
+    for i, t in enumerate(prompt):
+        cfg.prompt[i] = t
+    mk = ofa.Megakernel(cfg)
+    mk.load_weights(oracle.flatten(ocfg, w0))
+    mk.set_tokens(oracle.synthetic_tokens(ocfg.V, 1 << 14, 0))
+    for _ in range(6):
+        mk.run(40, timeout_ms=60000)
+    n = mk.decode_steps
+    assert n >= 7 + 8, n
+    n = min(n, 7 + 200)                          # enough to cross the 64-position context several times
+    got = [int(t) for t in mk.decode_tokens(n)[7:]]
+    want, _ = oracle.greedy_decode(ocfg, w0, prompt, len(got))
+    assert got == want
+    mk.close()

@@ -4,8 +4,8 @@ Some hosts of this library cannot call cudaMalloc where they need LayerNorm back
 another allocator's pool, or they run next to a resident persistent kernel that a device-wide allocation sync would
 stall. For them the entry point keeps its only scratch (the dgamma partials) in a fixed device array. This test drives it
 through the C ABI twice in a row - the second call with a smaller batch and the accumulate flag, so stale partials of the
-first call would show - and compares with the existing TK_LN_BWD + TK_LN_DG phases (caller-allocated partials) at the
-gradient tolerances the other GPU tests use. The file name sorts last on purpose: a run that stops at the first failure
+first call would show - and compares with the existing TK_LN_BWD + TK_LN_DG phases (caller-allocated partials), bit for bit
+(both run the same device function), and with autograd through F.layer_norm at the gradient tolerances the other GPU tests use. The file name sorts last on purpose: a run that stops at the first failure
 has then already executed every other test."""
 import ctypes as C
 
@@ -53,13 +53,22 @@ def _noalloc(ofa, dev, N, dg0, accumulate, use_dres):
 
 
 def test_noalloc_ln_backward_matches_scheduler_path_twice_in_a_row(ofa):
+    import torch.nn.functional as F
     for call, (N, accumulate, use_dres, seed) in enumerate([(4096, 0, False, 11), (528, 1, True, 12)]):
         dev = _inputs(ofa, N, seed)
         dg0 = np.full(D, 3.0, np.float32)
         dx_ref, dg_ref = _existing(ofa, dev, N, dg0, accumulate, use_dres)
         dx_new, dg_new = _noalloc(ofa, dev, N, dg0, accumulate, use_dres)
-        assert relmax(dx_new, dx_ref) <= 5e-2, f"call {call}: dx"
-        assert relmax(dg_new, dg_ref) <= 5e-3, f"call {call}: dgamma"
+        # both paths run the same device function on the same rows in the same order: identical bits, not merely close
+        np.testing.assert_array_equal(dx_new, dx_ref, err_msg=f"call {call}: dx")
+        np.testing.assert_array_equal(dg_new.view(np.uint32), dg_ref.view(np.uint32), err_msg=f"call {call}: dgamma")
+        # and both against autograd through F.layer_norm on the same (bf16-valued) inputs, at the tolerances of the other GPU tests
+        x = torch.from_numpy(dev["x"].download()).requires_grad_(); gm = torch.from_numpy(dev["gamma"].download()).requires_grad_()
+        F.layer_norm(x, (D,), gm, None, 1e-5).backward(torch.from_numpy(dev["dy"].download()))
+        want_dx = x.grad + (torch.from_numpy(dev["dres"].download()) if use_dres else 0)
+        want_dg = gm.grad + (torch.from_numpy(dg0) if accumulate else 0)
+        assert relmax(dx_new, want_dx.numpy()) <= 5e-2, f"call {call}: dx vs autograd"
+        assert relmax(dg_new, want_dg.numpy()) <= 5e-3, f"call {call}: dgamma vs autograd"
         assert np.all(np.isfinite(dx_new)) and np.all(np.isfinite(dg_new))
 
 
