@@ -53,7 +53,7 @@ template <int BN> struct Cfg {
 };
 // control area (1 KB at smem + BAR_OFFSET = the last 1,024 bytes of dynamic shared memory):
 //   [  0, 80) BN128: full[3] empty[3] accf[2] acce[2]     [ 80, 84) TMEM base slot     [ 96,104) serving fill barrier   [104,112) training bulk-copy barrier
-//   [128,160) scheduler hand-off words                      [176,224) BN256: full[2] empty[2] accf[1] acce[1]
+//   [128,160) scheduler hand-off words                      [176,224) BN256: full[2] empty[2] accf[1] acce[1]      [224,248) AdamW stage barriers [3]
 //   [256,512) and [512,768) two slots for phase descriptors: the one being worked on and the next phase's, fetched ahead
 //   [768,832) scheduling record (ticket range + dependencies) of the phase the scheduler thread looks at next
 template <int BN> __device__ __forceinline__ uint32_t bar_full(uint32_t base, int s) { return base + BAR_OFFSET + Cfg<BN>::BAR0 + 8u * s; }

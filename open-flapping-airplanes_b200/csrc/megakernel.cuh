@@ -31,7 +31,7 @@ template <class T> struct IsBf16 { static constexpr bool value = std::is_same<T,
 // ---------------------------------------------------------------------------------------------- one training task
 template <class T, int D, int DH>
 __device__ __forceinline__ void run_train_task(const Ctx& C, const PhaseDesc& d, int ph, int local, int step, unsigned char* smem,
-                                               gemm_tc::GemmPipe& gp, attn_tc::AttnPipe& ap, uint32_t& bulk_uses) {
+                                               gemm_tc::GemmPipe& gp, attn_tc::AttnPipe& ap, uint32_t& bulk_uses, uint32_t& adam_tiles) {
   const ModelDims& md = C.md;
   switch (d.kind) {
     case TK_DATA:
@@ -119,6 +119,14 @@ __device__ __forceinline__ void run_train_task(const Ctx& C, const PhaseDesc& d,
       break;
     case TK_ADAMW: {
       const ew::AdamHP hp = ew::adam_hp(C.hp, step + C.step_base);
+      if constexpr (IsBf16<T>::value) {               // inputs staged by the copy engine (the fp32 preset's blocks have no room for the stages)
+        const uint32_t bar0 = smem_u32(smem + C.smem_bytes - CTRL_BYTES + 224);
+        if (d.i2 == 0) {
+          if (d.i1) ew::adamw_task_bulk<T, bf16>(local, (float*)d.p[0], (const bf16*)d.p[1], (float*)d.p[2], (float*)d.p[3], (T*)d.p[4], d.n, hp, (const int2*)d.p[5], d.i0, smem, bar0, adam_tiles, C.status);
+          else ew::adamw_task_bulk<T, float>(local, (float*)d.p[0], (const float*)d.p[1], (float*)d.p[2], (float*)d.p[3], (T*)d.p[4], d.n, hp, (const int2*)d.p[5], d.i0, smem, bar0, adam_tiles, C.status);
+          break;
+        }
+      }
       if (d.i1) ew::adamw_task<T, bf16>(local, (float*)d.p[0], (const bf16*)d.p[1], (float*)d.p[2], (float*)d.p[3], (T*)d.p[4], d.n, hp, (const int2*)d.p[5], d.i0);
       else ew::adamw_task<T, float>(local, (float*)d.p[0], (const float*)d.p[1], (float*)d.p[2], (float*)d.p[3], (T*)d.p[4], d.n, hp, (const int2*)d.p[5], d.i0);
       break;
@@ -160,9 +168,16 @@ __device__ __forceinline__ void run_decode_task(const Ctx& C, const PhaseDesc& d
 
 // ---------------------------------------------------------------------------------------------- scheduler
 // Dependency wait of thread 0 (bounded). Returns 0 when every dependency of (step, ph) is satisfied, -2 when the block must
-// leave (job finished elsewhere, abort, or deadline).
-__device__ __forceinline__ int wait_deps(const Ctx& C, const Job& J, int job_id, int step, int ph, int local, const volatile int* rec) {
-  const int cnt = rec[2];
+// leave (job finished elsewhere, abort, or deadline). `R` is the phase's scheduling record (kernel parameter or shared memory).
+struct DepSet { int cnt; int ph[4], dl[4], nt[4]; };
+template <class RecPtr>
+__device__ __forceinline__ void load_deps(DepSet& d, RecPtr rec) {      // rec: int-indexable view of a SchedRec
+  d.cnt = rec[2];
+#pragma unroll
+  for (int k = 0; k < 4; k++) { d.ph[k] = rec[4 + 3 * k]; d.dl[k] = rec[5 + 3 * k]; d.nt[k] = rec[6 + 3 * k]; }
+}
+__device__ __forceinline__ int wait_deps(const Ctx& C, const Job& J, int job_id, int step, int ph, int local, const DepSet& R) {
+  const int cnt = R.cnt;
   const u64 t0 = gtimer();
   // a dependency may legitimately sit behind an external wait that is about to give up: its own bound is half as long again, so
   // that the status names the external flag that was never raised and not one of the tasks queued behind it
@@ -174,7 +189,7 @@ __device__ __forceinline__ int wait_deps(const Ctx& C, const Job& J, int job_id,
     int need[4]; const int* ctr[4];
 #pragma unroll
     for (int k = 0; k < 4; k++) {
-      const int p = k < cnt ? rec[4 + 3 * k] : 0, dl = k < cnt ? rec[5 + 3 * k] : 0, nt = k < cnt ? rec[6 + 3 * k] : 0;
+      const int p = k < cnt ? R.ph[k] : 0, dl = k < cnt ? R.dl[k] : 0, nt = k < cnt ? R.nt[k] : 0;
       ctr[k] = J.done + p; need[k] = k < cnt ? nt * (step + 1 + dl) : 0;
     }
     for (;;) {
@@ -225,6 +240,8 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
   volatile int* s_rec = reinterpret_cast<volatile int*>(ctrl + 768);
   const uint32_t s_rec_addr = smem_u32(ctrl + 768);
   int rec_ph = -1;                                  // thread 0: the phase whose record is (or is on its way) in s_rec
+  const SchedRec* prec = job_id == 0 ? C.train_rec : C.dec_rec;          // the same records inside the kernel parameter, when they fit
+  const bool ptab = (job_id == 0 ? C.train_rec_n : C.dec_rec_n) > 0;
   auto need_rec = [&](int p) {                      // thread 0: make s_rec hold phase p's record
     if (rec_ph != p) {
 #pragma unroll
@@ -241,7 +258,11 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
   const bool use_tc = IsBf16<T>::value && job_id == 0;
   attn_tc::AttnPipe ap; ap.tasks = ap.stages = ap.stages2 = ap.a = ap.b = ap.done = 0;
   uint32_t bulk_uses = 0;                            // uses of the block's bulk-copy barrier (control area byte 104)
-  if (use_tc) { if (tid == 0) mbar_init(smem_u32(ctrl + 104), 1); attn_tc::block_init(ap, smem); gemm_tc::block_init(gp, smem, C.status); }
+  uint32_t adam_tiles = 0;                           // tiles the block's AdamW tasks have staged (three barriers at control area byte 224)
+  if (use_tc) {
+    if (tid == 0) { mbar_init(smem_u32(ctrl + 104), 1); for (int q = 0; q < ew::ADAM_STAGES; q++) mbar_init(smem_u32(ctrl + 224 + 8 * q), 1); }
+    attn_tc::block_init(ap, smem); gemm_tc::block_init(gp, smem, C.status);
+  }
   // serving blocks: one mbarrier counts the bytes of the weight prefetch of the task they hold a ticket for
   const uint32_t fill_bar = smem_u32(ctrl + 96);
   uint32_t fills = 0;
@@ -271,10 +292,18 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
           // ticket range in registers and walk on, one scheduling record per phase passed. The record of the phase after
           // the one just worked on was requested at the end of the previous task and is normally already in shared memory.
           if (r < c_lo) { c_ph = -1; c_lo = 0; c_hi = 0; c_mul = 0; }        // a new step
-          while (r >= c_hi) {
-            c_ph++;
-            need_rec(c_ph);
-            c_lo = s_rec[0]; c_hi = s_rec[1]; c_mul = s_rec[3];
+          if (ptab) {                                    // records in the kernel parameter: a walk over constant memory
+            if (r >= c_hi) {
+              int p = c_ph + 1;
+              while (r >= prec[p].hi) p++;
+              c_ph = p; c_lo = prec[p].lo; c_hi = prec[p].hi; c_mul = prec[p].perm_mul;
+            }
+          } else {
+            while (r >= c_hi) {
+              c_ph++;
+              need_rec(c_ph);
+              c_lo = s_rec[0]; c_hi = s_rec[1]; c_mul = s_rec[3];
+            }
           }
           ph = c_ph; local = r - c_lo;
           // test hook (SchedRec::perm_mul, 0 in production): tickets of a phase are handed out in a permuted task order, which
@@ -282,8 +311,9 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
           if (c_mul) local = (int)(((long long)local * c_mul + (c_mul >> 1)) % (long long)(c_hi - c_lo));
           if (job_id == 0 && !(step == rstep && ph == rph)) {
             const u64 w0 = gtimer();
-            need_rec(ph);
-            res = wait_deps(C, J, job_id, step, ph, local, s_rec);
+            DepSet ds;
+            if (ptab) load_deps(ds, reinterpret_cast<const int*>(prec + ph)); else { need_rec(ph); load_deps(ds, s_rec); }
+            res = wait_deps(C, J, job_id, step, ph, local, ds);
             const u64 w = gtimer() - w0;
             waited += w;
             if (C.phase_busy && w > 200) atomicAdd(C.phase_busy + J.nph + ph, w);
@@ -318,7 +348,12 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
       filled = dec::prefetch<T, D, DH>(C.dp, C.md, d.kind, d.i0, local, smem, fill_bar);
       if (tid == 0) {
         int r2 = 0;
-        if (!(step == rstep && ph == rph)) { need_rec(ph); r2 = wait_deps(C, J, job_id, step, ph, local, s_rec); if (r2 == 0) { rstep = step; rph = ph; } }
+        if (!(step == rstep && ph == rph)) {
+          DepSet ds;
+          if (ptab) load_deps(ds, reinterpret_cast<const int*>(prec + ph)); else { need_rec(ph); load_deps(ds, s_rec); }
+          r2 = wait_deps(C, J, job_id, step, ph, local, ds);
+          if (r2 == 0) { rstep = step; rph = ph; }
+        }
         s_sel[4] = r2;
       }
       __syncthreads();
@@ -331,7 +366,7 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
     }
     u64 t0 = 0;
     if (tid == 0) { t0 = gtimer(); t_sync += t0 - tl1; if (job_id == 1 && C.dp.trace && local == 0 && (ph == 0 || ph == 2)) C.dp.trace[16 + ph] = t0; }
-    if (job_id == 0) run_train_task<T, D, DH>(C, d, ph, local, step, smem, gp, ap, bulk_uses);
+    if (job_id == 0) run_train_task<T, D, DH>(C, d, ph, local, step, smem, gp, ap, bulk_uses, adam_tiles);
     else run_decode_task<T, D, DH>(C, d, local, smem, fill_bar, fills & 1u);
     if (filled) fills++;
     __syncthreads();
@@ -342,7 +377,7 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
           sched_cp16(smem_u32(ctrl + 256 + 256 * (slot ^ 1)) + 16 * (tid - 1), reinterpret_cast<const char*>(J.ph + nxt) + 16 * (tid - 1));
         ahead_ph = nxt;
       }
-      if (tid == 0 && rec_ph != nxt) {
+      if (tid == 0 && !ptab && rec_ph != nxt) {
 #pragma unroll
         for (int q = 0; q < 4; q++) sched_cp16(s_rec_addr + 16 * q, reinterpret_cast<const char*>(J.rec + nxt) + 16 * q);
         rec_ph = nxt;

@@ -7,6 +7,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <cmath>
 #include <string>
@@ -40,6 +41,7 @@ struct DevJob {
   PhaseDesc* ph = nullptr; SchedRec* rec = nullptr; int *prefix = nullptr, *ntasks = nullptr, *dep_off = nullptr, *dep_cnt = nullptr; Dep* deps = nullptr;
   int* done = nullptr; unsigned* ticket = nullptr;
   int nph = 0;
+  std::vector<SchedRec> hrec;   // host copy of the scheduling records: they also travel inside the kernel parameter when they fit
   void free_all() {
     cudaFree(ph); cudaFree(rec); rec = nullptr; cudaFree(prefix); cudaFree(ntasks); cudaFree(dep_off); cudaFree(dep_cnt); cudaFree(deps); cudaFree(done); cudaFree(ticket);
     *this = DevJob();
@@ -214,11 +216,19 @@ bool upload_job(const std::vector<HostPhase>& ph, int last_phase, int nsteps, De
   cudaMemcpy(dj.dep_cnt, dcnt.data(), 4 * nph, cudaMemcpyHostToDevice);
   cudaMemcpy(dj.deps, deps.data(), sizeof(Dep) * deps.size(), cudaMemcpyHostToDevice);
   cudaMemset(dj.done, 0, 4 * nph); cudaMemset(dj.ticket, 0, 4);
-  dj.nph = nph;
+  dj.nph = nph; dj.hrec = rec;
   dj.j.nph = nph; dj.j.tasks_per_step = prefix[nph]; dj.j.nsteps = nsteps; dj.j.last_phase = last_phase;
   dj.j.ph = dj.ph; dj.j.prefix = dj.prefix; dj.j.ntasks = dj.ntasks; dj.j.dep_off = dj.dep_off; dj.j.dep_cnt = dj.dep_cnt; dj.j.deps = dj.deps; dj.j.rec = dj.rec;
   dj.j.done = dj.done; dj.j.ticket = dj.ticket;
   return true;
+}
+
+// copies a job's scheduling records into the kernel parameter when they fit
+void fill_param_records(Ctx& C, const DevJob* train, const DevJob* dec) {
+  C.train_rec_n = 0; C.dec_rec_n = 0;
+  if (getenv("OFA_B200_GLOBAL_RECS")) return;      // A/B switch for measurements: keep using the records in global memory
+  if (train && train->nph > 0 && train->nph <= PARAM_TRAIN_PH) { memcpy(C.train_rec, train->hrec.data(), sizeof(SchedRec) * train->nph); C.train_rec_n = train->nph; }
+  if (dec && dec->nph > 0 && dec->nph <= PARAM_DEC_PH) { memcpy(C.dec_rec, dec->hrec.data(), sizeof(SchedRec) * dec->nph); C.dec_rec_n = dec->nph; }
 }
 
 template <class T, int D, int DH> cudaError_t launch_kernel(const Ctx& C, int nblocks, int smem, cudaStream_t s) {
@@ -463,6 +473,7 @@ bool build_train_graph(ofa_ctx* c) {
       PhaseDesc d = mk(TK_ADAMW, (int)((n + ew::OPT_CHUNK - 1) / ew::OPT_CHUNK));
       d.p[0] = c->W32 + off; d.p[1] = G(off); d.p[2] = c->M32 + off; d.p[3] = c->V32 + off; d.p[4] = Wact + off;
       d.n = n; d.i0 = (int)nodecay.size(); d.i1 = gbf ? 1 : 0;
+      d.i2 = getenv("OFA_B200_ADAM_DIRECT") ? 1 : 0;     // A/B switch for measurements: 1 = the loop of direct loads instead of the staged inputs
       std::vector<int2> nd; for (const Span& sp : nodecay) nd.push_back(make_int2((int)(sp.off - off), (int)(sp.off - off + sp.n)));
       int2* dn = c->ar.alloc<int2>(std::max<size_t>(1, nd.size()));
       if (dn && !nd.empty()) c->ar.h2d(dn, nd.data(), nd.size() * sizeof(int2));
@@ -1031,6 +1042,7 @@ extern "C" int ofa_launch(ofa_ctx* c, int nsteps) {
   C.use_train = train_on ? 1 : 0;
   if (train_on) C.train = c->train_job.j;
   if (c->cfg.use_decode) C.dec = c->dec_job.j;
+  fill_param_records(C, train_on ? &c->train_job : nullptr, c->cfg.use_decode ? &c->dec_job : nullptr);
   C.data = c->d_tokens; C.ntok = c->ntok; C.starts = c->nstarts > 0 ? c->d_starts : nullptr; C.nstarts = c->nstarts;
   C.loss_hist = c->d_loss_hist ? c->d_loss_hist + c->steps_total : nullptr;   // history, LR schedule and data windows continue across launches
   C.step_done = c->d_step_done;
@@ -1270,8 +1282,10 @@ extern "C" int ofa_run_phases(int dtype, const ofa_dims* dims, const ofa_phase* 
   }
   P[0].deps.push_back(Dep{nph - 1, -1});
   if (!upload_job(P, nph - 1, repeats, dj, err)) { ar.free_all(); return fail(nullptr, OFA_BAD_ARGUMENT, err); }
-  Ctx C; memset(&C, 0, sizeof C);
+  static thread_local Ctx C;      // 31 KB: not on the stack
+  memset(&C, 0, sizeof C);
   C.train = dj.j; C.md = m;
+  fill_param_records(C, &dj, nullptr);
   if (adam) { C.hp.lr_max = adam[0]; C.hp.lr_min = adam[0]; C.hp.beta1 = adam[1]; C.hp.beta2 = adam[2]; C.hp.eps = adam[3]; C.hp.wd = adam[4]; C.hp.grad_scale = adam[5]; C.hp.constant_lr = 1; }
   C.train_sms = prop.multiProcessorCount; C.use_train = 1;
   C.status = ar.alloc<DevStatus>(1); C.finished = ar.alloc<int>(1); C.t_end = ar.alloc<unsigned long long>(1);

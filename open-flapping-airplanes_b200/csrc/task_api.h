@@ -83,6 +83,10 @@ struct alignas(16) SchedRec {
   int dep[12];              // per dependency: phase, step delta, task count of that phase
 };
 constexpr int CTRL_BYTES = 1024;   // control area at the end of every block's dynamic shared memory
+// The scheduling records of both jobs travel with the launch as part of the kernel parameter (constant bank): a block that
+// claims a ticket finds the phase and its dependencies without a single round trip to global memory. Jobs with more phases than
+// fit (the parameter is limited to 32,764 bytes) fall back to the records in global memory.
+constexpr int PARAM_TRAIN_PH = 400, PARAM_DEC_PH = 64;
 
 struct Job {
   int nph, tasks_per_step, nsteps, last_phase;
@@ -159,7 +163,11 @@ struct Ctx {
   unsigned long long dep_timeout_ns;
   int* blk_info;            // per block: %smid | role << 16 (1 serve, 2 reserved-idle, 3 train, 4 idle)
   int* arrived;             // blocks of this launch that have started (idle partitions leave only when all have)
-  int smem_bytes;           // dynamic shared memory per block; its last 512 bytes hold barriers (tensor-core path), the scheduler's hand-off words and the current phase descriptor
+  int smem_bytes;           // dynamic shared memory per block; its last 1,024 bytes are the control area (barriers, hand-off words, descriptor slots)
+  int train_rec_n, dec_rec_n;               // phases whose records are held below (0: use Job::rec in global memory)
+  SchedRec train_rec[PARAM_TRAIN_PH];
+  SchedRec dec_rec[PARAM_DEC_PH];
 };
+static_assert(sizeof(Ctx) <= 32764, "kernel parameter too large");
 
 }  // namespace ofa

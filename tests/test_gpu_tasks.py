@@ -121,8 +121,9 @@ def test_cross_entropy(ofa, K, bf, V):
     assert relmax(d_lg.download(), lgr.grad) <= (2e-2 if bf else 1e-5)
 
 
-@pytest.mark.parametrize("bf,gbf", [(True, False), (True, True), (False, False)])
-def test_adamw_three_steps(ofa, K, oracle, bf, gbf):
+@pytest.mark.parametrize("bf,gbf,direct", [(True, False, 0), (True, True, 0), (True, False, 1), (True, True, 1), (False, False, 0)])
+def test_adamw_three_steps(ofa, K, oracle, bf, gbf, direct):
+    """direct = 0: inputs staged through shared memory by bulk copies (bf16 path); 1: the loop of direct 16-byte loads"""
     dims = DIMS_S if bf else DIMS_T
     dt, dty = ("bf16", K.DTYPE_BF16) if bf else (np.float32, K.DTYPE_F32)
     n = 3 * 65536 + 1000
@@ -137,7 +138,7 @@ def test_adamw_three_steps(ofa, K, oracle, bf, gbf):
     # one launch per optimizer step so that each step sees its own gradient; the step counter restarts, so emulate with betas:
     # instead run the three steps as `repeats` over the SAME gradient and compare with the oracle fed the same gradient thrice
     dG.upload(Gs[0].numpy())
-    ofa.run_phases(dty, dims, [ofa.phase(K.TK_ADAMW, [dW, dG, dM, dV, dWa, dnd], n=n, i0=len(nd), i1=1 if gbf else 0)], repeats=3, adam=hp)
+    ofa.run_phases(dty, dims, [ofa.phase(K.TK_ADAMW, [dW, dG, dM, dV, dWa, dnd], n=n, i0=len(nd), i1=1 if gbf else 0, i2=direct)], repeats=3, adam=hp)
     Wr, mr, vr = oracle.adamw_ref(W0, [Gs[0]] * 3, nd, lr=hp[0], betas=(hp[1], hp[2]), eps=hp[3], wd=hp[4], grad_scale=hp[5])
     Wc = dW.download()
     assert relmax(Wc, Wr) <= 1e-5
