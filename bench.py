@@ -216,6 +216,7 @@ def main():
     dp = None
     if world > 1:
         cfg.dp_world, cfg.grad_bf16, cfg.ext_sync = world, 1, 1
+    cfg.sched_profile = 1 if args.phase_table else 0    # the in-kernel time tables are only read by --phase-table
     for kv in args.cfg:
         k, v = kv.split("=")
         if k not in [f[0] for f in cfg._fields_]:

@@ -67,6 +67,7 @@ typedef struct {
   int gemm_nsub;            /* consecutive 128-wide N tiles per GEMM task (0 = default)                           */
   double timeout_s;         /* device-side bound for a wait on an external flag (0 = default 20 s); waits for dependencies inside the graph give up after 1.5 x this */
   int device;               /* CUDA device ordinal; < 0 = planning context: layout, buckets and phase graphs are built and can be queried, nothing touches a device and nothing can be launched */
+  int sched_profile;        /* 1 (preset default): the kernel keeps the per-phase and per-block time tables that ofa_phase_info / ofa_phase_wait_ns / ofa_phase_window / ofa_read_block_busy / ofa_read_decode_trace report (the reference's report section, ofa.cu:722-746); 0: it does not (they read zero) and every task saves several timer reads and atomics. Step times, losses and live words are kept either way */
 } ofa_config;
 
 /* preset: "tiny" (the char-level fp32 model: vocab 65, d_model 64, 2 layers, 4 heads, context 64, batch 16) or "gpt_s" (the 162M bf16 model: vocab 50304 untied, d_model 768, 12 layers, 12 heads, context 1024, batch 4). */
@@ -128,6 +129,8 @@ int ofa_read_block_info(ofa_ctx* ctx, int* out, size_t n);
 int ofa_decode_phase_info(const ofa_ctx* ctx, int phase, char* name, size_t name_cap, int* ntasks, unsigned long long* busy_ns);
 /* dependencies of a phase: job 0 = training graph, 1 = serving graph; returns their number and fills up to cap (phase, step-delta) pairs (Job::deps, ofa.cu:103-105) */
 int ofa_phase_deps(const ofa_ctx* ctx, int job, int phase, int* dep_phase, int* dep_delta, int cap);
+/* grain of the dependencies of a training phase, in the order ofa_phase_deps lists them: grain[i] = 1 when the phase's tasks wait for that producer per 128-token row block (only for the producer tasks that write the rows they read) instead of for the whole producer phase, which is the reference's only grain (ofa.cu:245-255); rb_map = how the phase's own tasks map to row blocks (0: they do not). Returns the number of dependencies. */
+int ofa_phase_dep_grain(const ofa_ctx* ctx, int phase, int* rb_map, int* grain, int cap);
 int ofa_decode_steps(const ofa_ctx* ctx);                                  /* tokens processed by the serving job      */
 int ofa_read_decode_tokens(ofa_ctx* ctx, int* out, size_t cap);            /* the pinned ring: sampled ids, OFA_OUT_* markers, -1 = unused */
 int ofa_read_decode_logits(ofa_ctx* ctx, float* out, size_t n);            /* fp32 logits of the last decoded token    */

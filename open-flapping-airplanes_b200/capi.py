@@ -18,7 +18,7 @@ class Config(C.Structure):
         ("infer_sms", C.c_int), ("reserved_sms", C.c_int), ("train_sms", C.c_int), ("use_decode", C.c_int),
         ("n_prompt", C.c_int), ("prompt", C.c_int * 32), ("answer_len", C.c_int), ("temperature", C.c_float), ("decode_seed", C.c_ulonglong),
         ("decode_out_cap", C.c_int), ("dp_world", C.c_int), ("grad_bf16", C.c_int), ("ext_sync", C.c_int), ("bucket_bytes", C.c_int), ("attn_legacy", C.c_int), ("adam_interleave", C.c_int), ("head_dx_splitk", C.c_int),
-        ("gemm_nsub", C.c_int), ("timeout_s", C.c_double), ("device", C.c_int),
+        ("gemm_nsub", C.c_int), ("timeout_s", C.c_double), ("device", C.c_int), ("sched_profile", C.c_int),
     ]
 
 
@@ -75,6 +75,7 @@ PROTOTYPES = {
     "ofa_read_block_info": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t]),
     "ofa_decode_phase_info": (C.c_int, [C.c_void_p, C.c_int, C.c_char_p, C.c_size_t, C.POINTER(C.c_int), C.POINTER(C.c_ulonglong)]),
     "ofa_phase_deps": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int), C.c_int]),
+    "ofa_phase_dep_grain": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int), C.c_int]),
     "ofa_decode_steps": (C.c_int, [C.c_void_p]),
     "ofa_read_decode_tokens": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t]),
     "ofa_read_decode_logits": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t]),

@@ -169,14 +169,35 @@ __device__ __forceinline__ void run_decode_task(const Ctx& C, const PhaseDesc& d
 // ---------------------------------------------------------------------------------------------- scheduler
 // Dependency wait of thread 0 (bounded). Returns 0 when every dependency of (step, ph) is satisfied, -2 when the block must
 // leave (job finished elsewhere, abort, or deadline). `R` is the phase's scheduling record (kernel parameter or shared memory).
-struct DepSet { int cnt; int ph[4], dl[4], nt[4]; };
+struct DepSet { int cnt; int ph[4], dl[4], nt[4], gr[4]; int rb_off, rb_map; bool any_rb; };
 template <class RecPtr>
 __device__ __forceinline__ void load_deps(DepSet& d, RecPtr rec) {      // rec: int-indexable view of a SchedRec
-  d.cnt = rec[2];
+  d.cnt = rec[2]; d.rb_off = rec[4]; d.rb_map = rec[5];
+  d.any_rb = false;
 #pragma unroll
-  for (int k = 0; k < 4; k++) { d.ph[k] = rec[4 + 3 * k]; d.dl[k] = rec[5 + 3 * k]; d.nt[k] = rec[6 + 3 * k]; }
+  for (int k = 0; k < 4; k++) {
+    const int w = rec[6 + 2 * k];
+    d.ph[k] = w & 0xFFFF; d.dl[k] = (w & DEP_PREV) ? -1 : 0; d.gr[k] = (w & DEP_RB) ? 1 : 0; d.nt[k] = rec[7 + 2 * k];
+    d.any_rb = d.any_rb || (k < d.cnt && d.gr[k]);
+  }
 }
-__device__ __forceinline__ int wait_deps(const Ctx& C, const Job& J, int job_id, int step, int ph, int local, const DepSet& R) {
+// row block a task writes (prod) and the range of row blocks it reads from its row-block-grain producers [clo, chi]
+__device__ __forceinline__ void rb_of_task(int rb_map, const ModelDims& md, int local, int& prod, int& clo, int& chi) {
+  const int kind = rb_map & 0xFF, a = rb_map >> 8;
+  prod = clo = chi = 0;
+  if (kind == RB_MOD) prod = clo = chi = local % a;
+  else if (kind == RB_DIV) prod = clo = chi = local / a;
+  else if (kind == RB_ATT_FWD) {
+    const int BH = md.B * md.H, QT = md.T >> 7;
+    const int qt = QT - 1 - local / BH, b = (local % BH) / md.H;
+    prod = b * QT + qt; clo = b * QT; chi = prod;
+  } else if (kind == RB_ATT_BWD) {
+    const int BH = md.B * md.H, QT = md.T >> 7;
+    if (local < BH * QT) { const int kt = local / BH, b = (local % BH) / md.H; prod = b * QT + kt; clo = prod; chi = b * QT + QT - 1; }
+    else { const int l2 = local - BH * QT, qt = QT - 1 - l2 / BH, b = (l2 % BH) / md.H; prod = clo = chi = b * QT + qt; }
+  }
+}
+__device__ __forceinline__ int wait_deps(const Ctx& C, const Job& J, int job_id, int step, int ph, int local, const DepSet& R, const int* prod_rb_off) {
   const int cnt = R.cnt;
   const u64 t0 = gtimer();
   // a dependency may legitimately sit behind an external wait that is about to give up: its own bound is half as long again, so
@@ -186,19 +207,27 @@ __device__ __forceinline__ int wait_deps(const Ctx& C, const Job& J, int job_id,
   if (cnt >= 0) {
     // up to four dependencies from the phase's scheduling record: their counters are read with relaxed loads that are all in
     // flight together, and one acquire fence after the last successful check orders the task's reads behind them
-    int need[4]; const int* ctr[4];
+    int need[4]; const int* ctr[4]; int span[4];
+    int prod = 0, clo = 0, chi = 0;
+    if (R.any_rb) rb_of_task(R.rb_map, C.md, local, prod, clo, chi);
 #pragma unroll
     for (int k = 0; k < 4; k++) {
       const int p = k < cnt ? R.ph[k] : 0, dl = k < cnt ? R.dl[k] : 0, nt = k < cnt ? R.nt[k] : 0;
-      ctr[k] = J.done + p; need[k] = k < cnt ? nt * (step + 1 + dl) : 0;
+      const bool g = k < cnt && R.gr[k];
+      ctr[k] = g ? J.done_rb + prod_rb_off[k] + clo : J.done + p;
+      span[k] = g ? chi - clo + 1 : 1;
+      need[k] = k < cnt ? nt * (step + 1 + dl) : 0;
     }
     for (;;) {
-      int v[4];
-#pragma unroll
-      for (int k = 0; k < 4; k++) v[k] = need[k] > 0 ? ld_relaxed(ctr[k]) : 0;
       bool ready = true;
 #pragma unroll
-      for (int k = 0; k < 4; k++) ready = ready && v[k] >= need[k];
+      for (int k = 0; k < 4; k++) {
+        if (need[k] > 0) {
+          int v = ld_relaxed(ctr[k]);
+          for (int q = 1; q < span[k]; q++) v = min(v, ld_relaxed(ctr[k] + q));
+          ready = ready && v >= need[k];
+        }
+      }
       if (ready) { fence_acquire(); return 0; }
       if (job_id == 1 && C.use_train && ld_relaxed(C.finished)) return -2;
       if ((++spins & 63u) == 0) {
@@ -240,6 +269,7 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
   volatile int* s_rec = reinterpret_cast<volatile int*>(ctrl + 768);
   const uint32_t s_rec_addr = smem_u32(ctrl + 768);
   int rec_ph = -1;                                  // thread 0: the phase whose record is (or is on its way) in s_rec
+  const bool prof = (C.sched_flags & 2) != 0;        // per-phase and per-block time tables are kept (several %globaltimer reads and atomics per task)
   const SchedRec* prec = job_id == 0 ? C.train_rec : C.dec_rec;          // the same records inside the kernel parameter, when they fit
   const bool ptab = (job_id == 0 ? C.train_rec_n : C.dec_rec_n) > 0;
   auto need_rec = [&](int p) {                      // thread 0: make s_rec hold phase p's record
@@ -272,11 +302,13 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
     __syncthreads();
   }
   u64 waited = 0, t_claim = 0, t_sync = 0, t_tail = 0, tl0 = 0, tl1 = 0;   // thread 0: where the time outside tasks goes
+  bool c_any_rb = false;                             // thread 0: the phase last waited for has row-block dependencies (checked per task)
+  int c_rb_off = -1, c_rb_map = 0;                   // thread 0: where and how the cached phase counts its completions per row block
   int c_ph = -1, c_lo = 0, c_hi = 0, c_mul = 0;      // thread 0: cached phase, its ticket range [c_lo, c_hi) within a step, and its test-only task permutation
   unsigned next_g = 0; bool have_next = false; unsigned claims = 0;   // thread 0: the ticket taken at the end of the previous task
   for (;;) {
     if (tid == 0) {                                  // ---- claim (and, for the training job, wait for the dependencies)
-      tl0 = gtimer(); if (tl1) t_tail += tl0 - tl1;
+      if (prof) { tl0 = gtimer(); if (tl1) t_tail += tl0 - tl1; }
       const u64 w_before = waited;
       int res = 0, step = 0, ph = 0, local = 0;
       // the abort / finished words are looked at inside every wait loop; here only now and then, a claim should not pay for them
@@ -291,44 +323,53 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
           // A block's tickets grow, so within a step it only moves forward through the phases: keep the current phase's
           // ticket range in registers and walk on, one scheduling record per phase passed. The record of the phase after
           // the one just worked on was requested at the end of the previous task and is normally already in shared memory.
-          if (r < c_lo) { c_ph = -1; c_lo = 0; c_hi = 0; c_mul = 0; }        // a new step
+          if (r < c_lo) { c_ph = -1; c_lo = 0; c_hi = 0; c_mul = 0; c_any_rb = false; }        // a new step
           if (ptab) {                                    // records in the kernel parameter: a walk over constant memory
             if (r >= c_hi) {
               int p = c_ph + 1;
               while (r >= prec[p].hi) p++;
-              c_ph = p; c_lo = prec[p].lo; c_hi = prec[p].hi; c_mul = prec[p].perm_mul;
+              c_ph = p; c_lo = prec[p].lo; c_hi = prec[p].hi; c_mul = prec[p].perm_mul; c_rb_off = prec[p].rb_off; c_rb_map = prec[p].rb_map; c_any_rb = false;
             }
           } else {
             while (r >= c_hi) {
               c_ph++;
               need_rec(c_ph);
-              c_lo = s_rec[0]; c_hi = s_rec[1]; c_mul = s_rec[3];
+              c_lo = s_rec[0]; c_hi = s_rec[1]; c_mul = s_rec[3]; c_rb_off = s_rec[4]; c_rb_map = s_rec[5]; c_any_rb = false;
             }
           }
           ph = c_ph; local = r - c_lo;
           // test hook (SchedRec::perm_mul, 0 in production): tickets of a phase are handed out in a permuted task order, which
           // must not change any result - the reference's shuffled-order check (llm/gemm/test_gemm.cu:20-49)
           if (c_mul) local = (int)(((long long)local * c_mul + (c_mul >> 1)) % (long long)(c_hi - c_lo));
-          if (job_id == 0 && !(step == rstep && ph == rph)) {
-            const u64 w0 = gtimer();
-            DepSet ds;
+          // a phase whose dependencies are all phase-level stays ready once it has been seen ready; row-block dependencies are per task
+          if (job_id == 0 && (!(step == rstep && ph == rph) || c_any_rb)) {
+            const u64 w0 = prof ? gtimer() : 0;
+            DepSet ds; int pro[4] = {0, 0, 0, 0};
             if (ptab) load_deps(ds, reinterpret_cast<const int*>(prec + ph)); else { need_rec(ph); load_deps(ds, s_rec); }
-            res = wait_deps(C, J, job_id, step, ph, local, ds);
-            const u64 w = gtimer() - w0;
-            waited += w;
-            if (C.phase_busy && w > 200) atomicAdd(C.phase_busy + J.nph + ph, w);
+            if (ds.any_rb) {
+#pragma unroll
+              for (int k = 0; k < 4; k++) if (k < ds.cnt && ds.gr[k]) pro[k] = ptab ? prec[ds.ph[k]].rb_off : __ldg(&J.rec[ds.ph[k]].rb_off);
+            }
+            res = wait_deps(C, J, job_id, step, ph, local, ds, pro);
+            c_any_rb = ds.any_rb;
+            if (prof) {
+              const u64 w = gtimer() - w0;
+              waited += w;
+              if (C.phase_busy && w > 200) atomicAdd(C.phase_busy + J.nph + ph, w);
+            }
             if (res == 0) { rstep = step; rph = ph; }
           }
         }
       }
-      s_sel[0] = res; s_sel[1] = step; s_sel[2] = ph; s_sel[3] = local;
-      tl1 = gtimer(); t_claim += (tl1 - tl0) - (waited - w_before);
+      s_sel[0] = res; s_sel[1] = step; s_sel[2] = ph; s_sel[3] = local; s_sel[5] = c_rb_off; s_sel[6] = c_rb_map;
+      if (prof) { tl1 = gtimer(); t_claim += (tl1 - tl0) - (waited - w_before); }
     } else if (tid < 16) {
       sched_cp_wait();                               // the descriptor requested at the end of the last task: visible to all after the barrier below
     }
     __syncthreads();
     int res = s_sel[0];
     const int step = s_sel[1], ph = s_sel[2], local = s_sel[3];
+    const int t_rb_off = s_sel[5], t_rb_map = s_sel[6];      // read now: thread 0 runs ahead of the thread that signals and rewrites these words for the next task
     if (res < 0) break;
     // The descriptor is read from shared memory: every dependency check ends with a device-scope acquire, after which L1 no
     // longer holds it, and the chain of dependent global loads that decoding it would take was a measurable part of the
@@ -349,9 +390,9 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
       if (tid == 0) {
         int r2 = 0;
         if (!(step == rstep && ph == rph)) {
-          DepSet ds;
+          DepSet ds; int pro[4] = {0, 0, 0, 0};
           if (ptab) load_deps(ds, reinterpret_cast<const int*>(prec + ph)); else { need_rec(ph); load_deps(ds, s_rec); }
-          r2 = wait_deps(C, J, job_id, step, ph, local, ds);
+          r2 = wait_deps(C, J, job_id, step, ph, local, ds, pro);
           if (r2 == 0) { rstep = step; rph = ph; }
         }
         s_sel[4] = r2;
@@ -365,7 +406,9 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
       }
     }
     u64 t0 = 0;
-    if (tid == 0) { t0 = gtimer(); t_sync += t0 - tl1; if (job_id == 1 && C.dp.trace && local == 0 && (ph == 0 || ph == 2)) C.dp.trace[16 + ph] = t0; }
+    if (tid == 0) {
+      if (prof) { t0 = gtimer(); t_sync += t0 - tl1; if (job_id == 1 && C.dp.trace && local == 0 && (ph == 0 || ph == 2)) C.dp.trace[16 + ph] = t0; }
+    }
     if (job_id == 0) run_train_task<T, D, DH>(C, d, ph, local, step, smem, gp, ap, bulk_uses, adam_tiles);
     else run_decode_task<T, D, DH>(C, d, local, smem, fill_bar, fills & 1u);
     if (filled) fills++;
@@ -383,25 +426,36 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
         rec_ph = nxt;
       }
     }
+    // Two threads share the end of a task. Thread 0 takes the next ticket at once (a fetch-add whose value it needs only at the
+    // top of the loop: the task is finished, so holding the next ticket cannot delay anything this block still has to do, every
+    // dependency being a lower ticket). Thread 32 publishes the completion: ONE device-scope fence - the block barrier above
+    // ordered every thread's writes of this task before it - and relaxed increments of the completion counters. The fence waits
+    // for the SM's outstanding stores (about a microsecond after a GEMM epilogue); on its own thread it runs beside the ticket's
+    // round trip and the next claim instead of in front of them.
     if (tid == 0) {
-      // Completion signal first: a release at device scope after the block barrier orders every thread's writes of this task
-      // before it (no separate fence, and nobody waits for its round trip). The step's last phase needs the old value.
-      int old = -1;
-      if (ph == J.last_phase) { __threadfence(); old = atomicAdd(J.done + ph, 1); }
-      else red_release_add(J.done + ph, 1);
-      // Then take the next ticket: its round trip overlaps the bookkeeping below and the block hand-off. The task is finished,
-      // so holding the next ticket cannot delay anything this block still has to do (every dependency is a lower ticket).
-      next_g = atomicAdd(J.ticket, 1u); have_next = true;
-      const u64 t1 = gtimer(); tl1 = t1;
-      if (job_id == 1 && C.dp.trace && local == 0 && (ph == 0 || ph == 2)) C.dp.trace[17 + ph] = t1;
-      busy += t1 - t0;
-      if (job_id == 0 && C.phase_busy) {
-        atomicAdd(C.phase_busy + ph, t1 - t0);
-        if (step == C.prof_step) { atomicMin(C.phase_first + ph, t0); atomicMax(C.phase_last + ph, t1); }
+      if (!have_next) { next_g = atomicAdd(J.ticket, 1u); have_next = true; }
+      if (prof) {
+        const u64 t1 = gtimer(); tl1 = t1;
+        if (job_id == 1 && C.dp.trace && local == 0 && (ph == 0 || ph == 2)) C.dp.trace[17 + ph] = t1;
+        busy += t1 - t0;
+        if (job_id == 0 && C.phase_busy) {
+          atomicAdd(C.phase_busy + ph, t1 - t0);
+          if (step == C.prof_step) { atomicMin(C.phase_first + ph, t0); atomicMax(C.phase_last + ph, t1); }
+        }
+        if (job_id == 1 && C.dec_phase_busy) atomicAdd(C.dec_phase_busy + ph, t1 - t0);
       }
-      if (job_id == 1 && C.dec_phase_busy) atomicAdd(C.dec_phase_busy + ph, t1 - t0);
-      if (ph == J.last_phase && old == __ldg(J.ntasks + ph) * (step + 1) - 1) {     // last task of the step
-        if (job_id == 0) {
+    } else if (tid == 32) {
+      __threadfence();
+      const int rb_off = t_rb_off, rb_map = t_rb_map;
+      if (rb_off >= 0) {                               // completions per row block first: their waiters are the ones on the critical chain
+        int prod, clo, chi; rb_of_task(rb_map, C.md, local, prod, clo, chi);
+        red_relaxed_add(J.done_rb + rb_off + prod, 1);
+      }
+      if (ph != J.last_phase) red_relaxed_add(J.done + ph, 1);
+      else {                                           // the step's last phase needs the old value
+        const int old = atomicAdd(J.done + ph, 1);
+        if (job_id == 0 && old == __ldg(J.ntasks + ph) * (step + 1) - 1) {     // last task of the step
+          const u64 t1 = gtimer();
           C.step_done[step] = t1;
           if (C.live) C.live->steps = (unsigned)(step + 1);
           if (step == J.nsteps - 1) { *C.t_end = t1; __threadfence(); atomicExch(C.finished, 1); }

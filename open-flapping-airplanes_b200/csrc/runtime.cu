@@ -34,16 +34,17 @@ int shuffle_multiplier(unsigned seed, int phase, int n) {
   return 0;
 }
 
-struct HostPhase { std::string name; PhaseDesc d; std::vector<Dep> deps; };
+struct HostPhase { std::string name; PhaseDesc d; std::vector<Dep> deps; std::vector<char> rb_grain;   // per dependency: 1 = wait per 128-token row block instead of for the whole producer phase
+                   int rb_map = 0; };                                                                   // how this phase's tasks map to row blocks (RbKind | a << 8), 0 = they do not
 
 struct DevJob {
   Job j{};
   PhaseDesc* ph = nullptr; SchedRec* rec = nullptr; int *prefix = nullptr, *ntasks = nullptr, *dep_off = nullptr, *dep_cnt = nullptr; Dep* deps = nullptr;
-  int* done = nullptr; unsigned* ticket = nullptr;
+  int* done = nullptr; int* done_rb = nullptr; unsigned* ticket = nullptr;
   int nph = 0;
   std::vector<SchedRec> hrec;   // host copy of the scheduling records: they also travel inside the kernel parameter when they fit
   void free_all() {
-    cudaFree(ph); cudaFree(rec); rec = nullptr; cudaFree(prefix); cudaFree(ntasks); cudaFree(dep_off); cudaFree(dep_cnt); cudaFree(deps); cudaFree(done); cudaFree(ticket);
+    cudaFree(ph); cudaFree(rec); rec = nullptr; cudaFree(prefix); cudaFree(ntasks); cudaFree(dep_off); cudaFree(dep_cnt); cudaFree(deps); cudaFree(done); cudaFree(done_rb); cudaFree(ticket);
     *this = DevJob();
   }
 };
@@ -178,7 +179,8 @@ void prepare_gemm_f32(PhaseDesc& d) {
   d.g.nsub = 1;
 }
 
-bool upload_job(const std::vector<HostPhase>& ph, int last_phase, int nsteps, DevJob& dj, std::string& err) {
+// nrb = number of 128-token row blocks (0: no phase counts completions per row block, every dependency is phase-level)
+bool upload_job(const std::vector<HostPhase>& ph, int last_phase, int nsteps, DevJob& dj, std::string& err, int nrb = 0) {
   const int nph = (int)ph.size();
   std::vector<PhaseDesc> pd(nph); std::vector<int> prefix(nph + 1, 0), nt(nph), doff(nph), dcnt(nph); std::vector<Dep> deps;
   for (int i = 0; i < nph; i++) {
@@ -191,6 +193,16 @@ bool upload_job(const std::vector<HostPhase>& ph, int last_phase, int nsteps, De
     if (nt[i] <= 0) { err = "phase without tasks: " + ph[i].name; return false; }
   }
   if ((double)prefix[nph] * (double)nsteps >= 4.0e9) { err = "ticket counter would overflow"; return false; }
+  if (nph >= 65536) { err = "too many phases"; return false; }
+  // which phases count their completions per row block: those that say how their tasks map to row blocks, have a whole number of
+  // tasks per row block, and are waited for at that grain by somebody
+  std::vector<int> rb_off(nph, -1); int rb_total = 0;
+  if (nrb > 0 && !getenv("OFA_B200_PHASE_DEPS"))           // A/B switch for measurements: phase-level dependencies only
+    for (int i = 0; i < nph; i++)
+      for (size_t k = 0; k < ph[i].deps.size() && ph[i].deps.size() <= 4; k++) {
+        const int p = ph[i].deps[k].phase;
+        if (k < ph[i].rb_grain.size() && ph[i].rb_grain[k] && ph[i].rb_map && ph[p].rb_map && nt[p] % nrb == 0 && rb_off[p] < 0) { rb_off[p] = rb_total; rb_total += nrb; }
+      }
   std::vector<SchedRec> rec(nph);
   for (int i = 0; i < nph; i++) {
     SchedRec& r = rec[i]; memset(&r, 0, sizeof(r));
@@ -198,7 +210,13 @@ bool upload_job(const std::vector<HostPhase>& ph, int last_phase, int nsteps, De
     const int n = (int)ph[i].deps.size();
     r.ndeps = n <= 4 ? n : -1;
     r.perm_mul = shuffle_multiplier(g_task_shuffle_seed, i, nt[i]);
-    for (int k = 0; k < n && n <= 4; k++) { r.dep[3 * k] = ph[i].deps[k].phase; r.dep[3 * k + 1] = ph[i].deps[k].delta; r.dep[3 * k + 2] = nt[ph[i].deps[k].phase]; }
+    r.rb_off = rb_off[i]; r.rb_map = ph[i].rb_map;
+    for (int k = 0; k < n && n <= 4; k++) {
+      const Dep& e = ph[i].deps[k];
+      const bool rb = k < (int)ph[i].rb_grain.size() && ph[i].rb_grain[k] && ph[i].rb_map && rb_off[e.phase] >= 0;
+      r.dep[2 * k] = e.phase | (e.delta == -1 ? DEP_PREV : 0) | (rb ? DEP_RB : 0);
+      r.dep[2 * k + 1] = rb ? nt[e.phase] / nrb : nt[e.phase];
+    }
   }
   if (deps.empty()) deps.push_back(Dep{0, 0});
   dj.free_all();
@@ -206,7 +224,7 @@ bool upload_job(const std::vector<HostPhase>& ph, int last_phase, int nsteps, De
             cudaMalloc(&dj.ntasks, 4 * nph) == cudaSuccess && cudaMalloc(&dj.dep_off, 4 * nph) == cudaSuccess &&
             cudaMalloc(&dj.dep_cnt, 4 * nph) == cudaSuccess && cudaMalloc(&dj.deps, sizeof(Dep) * deps.size()) == cudaSuccess &&
             cudaMalloc(&dj.done, 4 * nph) == cudaSuccess && cudaMalloc(&dj.ticket, 4) == cudaSuccess &&
-            cudaMalloc(&dj.rec, sizeof(SchedRec) * nph) == cudaSuccess;
+            cudaMalloc(&dj.rec, sizeof(SchedRec) * nph) == cudaSuccess && cudaMalloc(&dj.done_rb, 4 * (size_t)std::max(1, rb_total)) == cudaSuccess;
   if (!ok) { err = "cudaMalloc failed (job tables)"; return false; }
   cudaMemcpy(dj.ph, pd.data(), sizeof(PhaseDesc) * nph, cudaMemcpyHostToDevice);
   cudaMemcpy(dj.rec, rec.data(), sizeof(SchedRec) * nph, cudaMemcpyHostToDevice);
@@ -215,17 +233,18 @@ bool upload_job(const std::vector<HostPhase>& ph, int last_phase, int nsteps, De
   cudaMemcpy(dj.dep_off, doff.data(), 4 * nph, cudaMemcpyHostToDevice);
   cudaMemcpy(dj.dep_cnt, dcnt.data(), 4 * nph, cudaMemcpyHostToDevice);
   cudaMemcpy(dj.deps, deps.data(), sizeof(Dep) * deps.size(), cudaMemcpyHostToDevice);
-  cudaMemset(dj.done, 0, 4 * nph); cudaMemset(dj.ticket, 0, 4);
+  cudaMemset(dj.done, 0, 4 * nph); cudaMemset(dj.ticket, 0, 4); cudaMemset(dj.done_rb, 0, 4 * (size_t)std::max(1, rb_total));
   dj.nph = nph; dj.hrec = rec;
   dj.j.nph = nph; dj.j.tasks_per_step = prefix[nph]; dj.j.nsteps = nsteps; dj.j.last_phase = last_phase;
   dj.j.ph = dj.ph; dj.j.prefix = dj.prefix; dj.j.ntasks = dj.ntasks; dj.j.dep_off = dj.dep_off; dj.j.dep_cnt = dj.dep_cnt; dj.j.deps = dj.deps; dj.j.rec = dj.rec;
-  dj.j.done = dj.done; dj.j.ticket = dj.ticket;
+  dj.j.done = dj.done; dj.j.done_rb = dj.done_rb; dj.j.ticket = dj.ticket;
   return true;
 }
 
 // copies a job's scheduling records into the kernel parameter when they fit
 void fill_param_records(Ctx& C, const DevJob* train, const DevJob* dec) {
   C.train_rec_n = 0; C.dec_rec_n = 0;
+  C.sched_flags = 0;
   if (getenv("OFA_B200_GLOBAL_RECS")) return;      // A/B switch for measurements: keep using the records in global memory
   if (train && train->nph > 0 && train->nph <= PARAM_TRAIN_PH) { memcpy(C.train_rec, train->hrec.data(), sizeof(SchedRec) * train->nph); C.train_rec_n = train->nph; }
   if (dec && dec->nph > 0 && dec->nph <= PARAM_DEC_PH) { memcpy(C.dec_rec, dec->hrec.data(), sizeof(SchedRec) * dec->nph); C.dec_rec_n = dec->nph; }
@@ -336,14 +355,28 @@ bool build_train_graph(ofa_ctx* c) {
   std::vector<std::vector<std::string>> prevdeps;   // cross-step dependencies by name (targets may be defined later)
   std::string err;
   bool ok = true;
-  auto addp = [&](const std::string& name, const PhaseDesc& d, std::vector<std::string> deps0, std::vector<std::string> deps_prev) {
-    HostPhase hp; hp.name = name; hp.d = d;
+  // how a phase's tasks map to 128-token row blocks (tensor-core path only: its row counts are multiples of 128)
+  const bool rb_ok = bf && m.N % 128 == 0 && m.T % 128 == 0;
+  auto rbmap = [&](const PhaseDesc& d) -> int {
+    if (!rb_ok) return 0;
+    switch (d.kind) {
+      case TK_GEMM: return (d.layout != GL_TN && d.g.M == (int)N && d.tiles_m == (int)N / 128) ? (RB_MOD | d.tiles_m << 8) : 0;
+      case TK_LN_FWD: case TK_LN_BWD: case TK_EMBED: return RB_DIV | (128 / ew::ROWS_PER_TASK) << 8;
+      case TK_CE: return RB_DIV | (128 / ew::CE_ROWS) << 8;
+      case TK_ATT_FWD: return RB_ATT_FWD;
+      case TK_ATT_BWD: return RB_ATT_BWD;
+      default: return 0;
+    }
+  };
+  // rbdeps: those of deps0 that are waited for per row block (the consumer task reads only the rows of its own row blocks)
+  auto addp = [&](const std::string& name, const PhaseDesc& d, std::vector<std::string> deps0, std::vector<std::string> deps_prev, std::vector<std::string> rbdeps = {}) {
+    HostPhase hp; hp.name = name; hp.d = d; hp.rb_map = rbmap(d);
     for (const std::string& e : deps0) {
       if (e.empty()) continue;
       auto it = id.find(e);
       if (it == id.end()) { ok = false; err = "unknown dependency " + e + " of " + name; continue; }
       bool dup = false; for (const Dep& x : hp.deps) dup = dup || x.phase == it->second;
-      if (!dup) hp.deps.push_back(Dep{it->second, 0});
+      if (!dup) { hp.deps.push_back(Dep{it->second, 0}); hp.rb_grain.push_back(std::find(rbdeps.begin(), rbdeps.end(), e) != rbdeps.end() ? 1 : 0); }
     }
     id[name] = (int)P.size();
     P.push_back(hp);
@@ -408,21 +441,21 @@ bool build_train_graph(ofa_ctx* c) {
   for (int l = 0; l < L; l++) {
     const std::string s = "L" + std::to_string(l) + " ";
     { PhaseDesc d = mk(TK_LN_FWD, rows16); d.p[0] = ln1[l]; d.p[1] = mean1[l]; d.p[2] = rstd1[l]; d.p[3] = xs[l]; d.p[4] = Wact + lay.g1[l];
-      addp(s + "ln1", d, {prev}, {opt_layer(l)}); }
-    addp(s + "qkv", mkgemm(GL_NN, GE_STORE, ln1[l], D, Wact + lay.wqkv[l], 3 * D, qkv[l], 3 * D, nullptr, 0, N, 3 * D, D, 0), {s + "ln1"}, {});
+      addp(s + "ln1", d, {prev}, {opt_layer(l)}, {prev}); }
+    addp(s + "qkv", mkgemm(GL_NN, GE_STORE, ln1[l], D, Wact + lay.wqkv[l], 3 * D, qkv[l], 3 * D, nullptr, 0, N, 3 * D, D, 0), {s + "ln1"}, {}, {s + "ln1"});
     { PhaseDesc d = mk(TK_ATT_FWD, attn_fwd_tasks); d.p[0] = qkv[l]; d.p[1] = att[l]; d.p[2] = lse[l];
       if (bf && !cfg.attn_legacy) { std::string e; d.p[6] = const_cast<void*>(make_attn_maps(c->ar, qkv[l], nullptr, N, D, e)); if (!d.p[6]) { ok = false; err = e; } }
-      addp(s + "attn", d, {s + "qkv"}, {}); }
-    addp(s + "wo+res", mkgemm(GL_NN, GE_RES, att[l], D, Wact + lay.wo[l], D, hb[l], D, xs[l], D, N, D, D, 0), {s + "attn"}, {});
+      addp(s + "attn", d, {s + "qkv"}, {}, {s + "qkv"}); }
+    addp(s + "wo+res", mkgemm(GL_NN, GE_RES, att[l], D, Wact + lay.wo[l], D, hb[l], D, xs[l], D, N, D, D, 0), {s + "attn"}, {}, {s + "attn"});
     { PhaseDesc d = mk(TK_LN_FWD, rows16); d.p[0] = ln2[l]; d.p[1] = mean2[l]; d.p[2] = rstd2[l]; d.p[3] = hb[l]; d.p[4] = Wact + lay.g2[l];
-      addp(s + "ln2", d, {s + "wo+res"}, {}); }
-    addp(s + "up+gelu", mkgemm(GL_NN, GE_GELU, ln2[l], D, Wact + lay.wup[l], FF, uact[l], FF, upre[l], FF, N, FF, D, 0), {s + "ln2"}, {});
-    addp(s + "down+res", mkgemm(GL_NN, GE_RES, uact[l], FF, Wact + lay.wdn[l], D, xs[l + 1], D, hb[l], D, N, D, FF, 0), {s + "up+gelu"}, {});
+      addp(s + "ln2", d, {s + "wo+res"}, {}, {s + "wo+res"}); }
+    addp(s + "up+gelu", mkgemm(GL_NN, GE_GELU, ln2[l], D, Wact + lay.wup[l], FF, uact[l], FF, upre[l], FF, N, FF, D, 0), {s + "ln2"}, {}, {s + "ln2"});
+    addp(s + "down+res", mkgemm(GL_NN, GE_RES, uact[l], FF, Wact + lay.wdn[l], D, xs[l + 1], D, hb[l], D, N, D, FF, 0), {s + "up+gelu"}, {}, {s + "up+gelu"});
     prev = s + "down+res";
   }
   { PhaseDesc d = mk(TK_LN_FWD, rows16); d.p[0] = lnf; d.p[1] = meanf; d.p[2] = rstdf; d.p[3] = xs[L]; d.p[4] = Wact + lay.gf;
-    addp("lnf", d, {prev}, {fwd_only ? "" : "head dW"}); }
-  addp("logits", mkgemm(GL_NT, GE_STORE, lnf, D, Wact + lay.head, D, logits, V, nullptr, 0, N, V, D, 0), {"lnf"}, {opt_head});
+    addp("lnf", d, {prev}, {fwd_only ? "" : "head dW"}, {prev}); }
+  addp("logits", mkgemm(GL_NT, GE_STORE, lnf, D, Wact + lay.head, D, logits, V, nullptr, 0, N, V, D, 0), {"lnf"}, {opt_head}, {"lnf"});
   std::vector<std::string> end_deps;
   if (fwd_only) {
     end_deps = {"logits"};
@@ -430,7 +463,7 @@ bool build_train_graph(ofa_ctx* c) {
     { PhaseDesc d = mk(TK_CE, (int)((N + ew::CE_ROWS - 1) / ew::CE_ROWS)); d.p[0] = logits; d.p[1] = c->C.tok_tgt; d.p[2] = lossv;
       const size_t usable = (size_t)((bf ? gemm_tc::BAR_OFFSET : c->smem - CTRL_BYTES) - 64);
       d.i0 = (int)(std::min(usable, V * sizeof(T)) / 16 * 16);
-      addp("cross-entropy", d, {"logits", "data"}, {}); }
+      addp("cross-entropy", d, {"logits", "data"}, {}, {"logits"}); }
     { PhaseDesc d = mk(TK_CE_MEAN, 1); d.p[0] = meanloss; d.p[1] = lossv; addp("loss mean", d, {"cross-entropy"}, {}); }
 
     // ---- gradient buckets (only used with ext_sync): head | layer groups from the top | wte+wpe
@@ -537,8 +570,8 @@ bool build_train_graph(ofa_ctx* c) {
       }
       in_trickle = false;
     };
-    auto addb = [&](const std::string& name, const PhaseDesc& d, std::vector<std::string> deps0, std::vector<std::string> deps_prev) {
-      addp(name, d, deps0, deps_prev);
+    auto addb = [&](const std::string& name, const PhaseDesc& d, std::vector<std::string> deps0, std::vector<std::string> deps_prev, std::vector<std::string> rbdeps = {}) {
+      addp(name, d, deps0, deps_prev, rbdeps);
       trickle(false);
     };
 
@@ -549,7 +582,7 @@ bool build_train_graph(ofa_ctx* c) {
       // it measured 1.2 % slower per step, the long tiles run beside head dW and are not what the step waits for.
       int S = 1;
       if (bf && V >= 8192 && cfg.head_dx_splitk) for (int c = 4; c >= 2; c--) if (V % (64 * (size_t)c) == 0) { S = c; break; }
-      if (S == 1) addp("head dX", mkgemm(GL_NN, GE_STORE, logits, V, Wact + lay.head, D, dxf, D, nullptr, 0, N, D, V, 0), {"cross-entropy"}, {});
+      if (S == 1) addp("head dX", mkgemm(GL_NN, GE_STORE, logits, V, Wact + lay.head, D, dxf, D, nullptr, 0, N, D, V, 0), {"cross-entropy"}, {}, {"cross-entropy"});
       else {
         const size_t Ks = V / S;
         std::vector<std::string> parts;
@@ -569,25 +602,25 @@ bool build_train_graph(ofa_ctx* c) {
     if (trickle_n && !lay.tied) { AdamItem it; it.name = "adamw head"; it.off = lay.head; it.n = V * D; it.deps = {"head dW", "head dX"}; adam_q.push_back(it); }
     if (ext && !lay.tied) signal(0);
     { PhaseDesc d = mk(TK_LN_BWD, rows16); d.p[0] = dxs[L]; d.p[1] = dgpf; d.p[2] = dxf; d.p[3] = xs[L]; d.p[4] = meanf; d.p[5] = rstdf; d.p[6] = Wact + lay.gf; d.p[7] = nullptr;
-      addb("lnf bwd", d, {"head dX"}, {}); }
+      addb("lnf bwd", d, {"head dX"}, {}, {"head dX"}); }
     auto mkdg = [&](float* part, size_t goff) { PhaseDesc d = mk(TK_LN_DG, (int)((D + NTHR - 1) / NTHR)); d.p[0] = G(goff); d.p[1] = part; d.i0 = 0; d.i1 = gbf ? 1 : 0; return d; };
     addb("lnf dgamma", mkdg(dgpf, lay.gf), {"lnf bwd"}, {});
     std::string g = "lnf bwd";
     const int attn_bwd_tasks = bf ? 2 * attn_fwd_tasks : m.B * m.H;
     for (int l = L - 1; l >= 0; l--) {
       const std::string s = "L" + std::to_string(l) + " ";
-      addb(s + "dpre", mkgemm(GL_NT, GE_DGELU, dxs[l + 1], D, Wact + lay.wdn[l], D, dpre[l], FF, upre[l], FF, N, FF, D, 0), {g}, {});
+      addb(s + "dpre", mkgemm(GL_NT, GE_DGELU, dxs[l + 1], D, Wact + lay.wdn[l], D, dpre[l], FF, upre[l], FF, N, FF, D, 0), {g}, {}, {g});
       addb(s + "dWdown", mkgemm(GL_TN, wepi, uact[l], FF, dxs[l + 1], D, G(lay.wdn[l]), D, nullptr, 0, FF, D, N, 0), {g}, {});
       if (interleave_adam) { if (l == L - 1) { if (!lay.tied) emit_adam_head(); } else emit_adam_layer(l + 1); }
-      addb(s + "dln2", mkgemm(GL_NT, GE_STORE, dpre[l], FF, Wact + lay.wup[l], FF, dln2[l], D, nullptr, 0, N, D, FF, 0), {s + "dpre"}, {});
+      addb(s + "dln2", mkgemm(GL_NT, GE_STORE, dpre[l], FF, Wact + lay.wup[l], FF, dln2[l], D, nullptr, 0, N, D, FF, 0), {s + "dpre"}, {}, {s + "dpre"});
       addb(s + "dWup", mkgemm(GL_TN, wepi, ln2[l], D, dpre[l], FF, G(lay.wup[l]), FF, nullptr, 0, D, FF, N, 0), {s + "dpre"}, {});
       { PhaseDesc d = mk(TK_LN_BWD, rows16); d.p[0] = dh[l]; d.p[1] = dgp2[l]; d.p[2] = dln2[l]; d.p[3] = hb[l]; d.p[4] = mean2[l]; d.p[5] = rstd2[l]; d.p[6] = Wact + lay.g2[l]; d.p[7] = dxs[l + 1];
-        addb(s + "ln2 bwd", d, {s + "dln2"}, {}); }
+        addb(s + "ln2 bwd", d, {s + "dln2"}, {}, {s + "dln2"}); }
       addb(s + "dgamma2", mkdg(dgp2[l], lay.g2[l]), {s + "ln2 bwd"}, {});
       if (bf) {   // the epilogue also forms the row term of attention backward, D[b,h,t] = sum_d dO * O: no separate pass over dO and O
         PhaseDesc d = mkgemm(GL_NT, GE_DR, dh[l], D, Wact + lay.wo[l], D, dob[l], D, att[l], D, N, D, D, 0);
         d.g.dr = Dr[l]; d.g.dr_T = m.T; d.g.dr_H = m.H;
-        addb(s + "dO", d, {s + "ln2 bwd"}, {});
+        addb(s + "dO", d, {s + "ln2 bwd"}, {}, {s + "ln2 bwd"});
       } else {
         addb(s + "dO", mkgemm(GL_NT, GE_STORE, dh[l], D, Wact + lay.wo[l], D, dob[l], D, nullptr, 0, N, D, D, 0), {s + "ln2 bwd"}, {});
       }
@@ -595,11 +628,11 @@ bool build_train_graph(ofa_ctx* c) {
       if (!bf) { PhaseDesc d = mk(TK_ATT_PREP, 1); d.p[0] = att[l]; d.p[1] = dob[l]; d.p[2] = Dr[l]; addb(s + "attn prep", d, {s + "dO"}, {}); }
       { PhaseDesc d = mk(TK_ATT_BWD, attn_bwd_tasks); d.p[0] = qkv[l]; d.p[1] = dob[l]; d.p[2] = lse[l]; d.p[3] = Dr[l]; d.p[4] = dqkv[l]; d.p[5] = att[l];
         if (bf && !cfg.attn_legacy) { std::string e; d.p[6] = const_cast<void*>(make_attn_maps(c->ar, qkv[l], dob[l], N, D, e)); if (!d.p[6]) { ok = false; err = e; } }
-        addb(s + "attn bwd", d, {bf ? s + "dO" : s + "attn prep"}, {}); }
-      addb(s + "dln1", mkgemm(GL_NT, GE_STORE, dqkv[l], 3 * D, Wact + lay.wqkv[l], 3 * D, dln1[l], D, nullptr, 0, N, D, 3 * D, 0), {s + "attn bwd"}, {});
+        addb(s + "attn bwd", d, {bf ? s + "dO" : s + "attn prep"}, {}, {s + "dO"}); }
+      addb(s + "dln1", mkgemm(GL_NT, GE_STORE, dqkv[l], 3 * D, Wact + lay.wqkv[l], 3 * D, dln1[l], D, nullptr, 0, N, D, 3 * D, 0), {s + "attn bwd"}, {}, {s + "attn bwd"});
       addb(s + "dWqkv", mkgemm(GL_TN, wepi, ln1[l], D, dqkv[l], 3 * D, G(lay.wqkv[l]), 3 * D, nullptr, 0, D, 3 * D, N, 0), {s + "attn bwd"}, {});
       { PhaseDesc d = mk(TK_LN_BWD, rows16); d.p[0] = dxs[l]; d.p[1] = dgp1[l]; d.p[2] = dln1[l]; d.p[3] = xs[l]; d.p[4] = mean1[l]; d.p[5] = rstd1[l]; d.p[6] = Wact + lay.g1[l]; d.p[7] = dh[l];
-        addb(s + "ln1 bwd", d, {s + "dln1"}, {}); }
+        addb(s + "ln1 bwd", d, {s + "dln1"}, {}, {s + "dln1"}); }
       addb(s + "dgamma1", mkdg(dgp1[l], lay.g1[l]), {s + "ln1 bwd"}, {});
       g = s + "ln1 bwd";
       if (trickle_n) {
@@ -764,6 +797,7 @@ extern "C" int ofa_default_config(ofa_config* cfg, const char* preset) {
   if (!cfg || !preset) return OFA_BAD_ARGUMENT;
   memset(cfg, 0, sizeof *cfg);
   cfg->beta1 = 0.9f; cfg->beta2 = 0.95f; cfg->eps = 1e-8f; cfg->weight_decay = 0.1f;
+  cfg->sched_profile = 1;
   cfg->dp_world = 1; cfg->temperature = 0.f; cfg->decode_seed = 1234; cfg->data_seed = 0; cfg->decode_out_cap = 65536;
   if (!strcmp(preset, "tiny")) {
     cfg->vocab = 65; cfg->d_model = 64; cfg->n_layer = 2; cfg->n_head = 4; cfg->ctx_len = 64; cfg->batch = 16; cfg->valid_vocab = 65;
@@ -1018,7 +1052,7 @@ extern "C" int ofa_launch(ofa_ctx* c, int nsteps) {
   cudaSetDevice(c->device);
   std::string err;
   if (train_on) {
-    if (!upload_job(c->train_ph, c->train_last, nsteps, c->train_job, err)) return fail(c, OFA_BAD_CONFIG, err);
+    if (!upload_job(c->train_ph, c->train_last, nsteps, c->train_job, err, (c->bf && c->md.N % 128 == 0) ? c->md.N / 128 : 0)) return fail(c, OFA_BAD_CONFIG, err);
     if (c->steps_total + nsteps > c->loss_cap) {
       const int cap = std::max(4096, 2 * (c->steps_total + nsteps));
       float* nl = c->ar.alloc<float>(cap);
@@ -1043,6 +1077,7 @@ extern "C" int ofa_launch(ofa_ctx* c, int nsteps) {
   if (train_on) C.train = c->train_job.j;
   if (c->cfg.use_decode) C.dec = c->dec_job.j;
   fill_param_records(C, train_on ? &c->train_job : nullptr, c->cfg.use_decode ? &c->dec_job : nullptr);
+  if (c->cfg.sched_profile) C.sched_flags |= 2;
   C.data = c->d_tokens; C.ntok = c->ntok; C.starts = c->nstarts > 0 ? c->d_starts : nullptr; C.nstarts = c->nstarts;
   C.loss_hist = c->d_loss_hist ? c->d_loss_hist + c->steps_total : nullptr;   // history, LR schedule and data windows continue across launches
   C.step_done = c->d_step_done;
@@ -1184,6 +1219,14 @@ extern "C" int ofa_phase_deps(const ofa_ctx* c, int job, int phase, int* dep_pha
   for (int i = 0; i < n && i < cap; i++) { if (dep_phase) dep_phase[i] = P[phase].deps[i].phase; if (dep_delta) dep_delta[i] = P[phase].deps[i].delta; }
   return n;
 }
+extern "C" int ofa_phase_dep_grain(const ofa_ctx* c, int phase, int* rb_map, int* grain, int cap) {
+  if (!c || phase < 0 || phase >= (int)c->train_ph.size()) return -1;
+  const HostPhase& p = c->train_ph[phase];
+  if (rb_map) *rb_map = p.rb_map;
+  const int n = (int)p.deps.size();
+  for (int i = 0; i < n && i < cap; i++) if (grain) grain[i] = (i < (int)p.rb_grain.size() && p.rb_grain[i] && p.rb_map && c->train_ph[p.deps[i].phase].rb_map) ? 1 : 0;
+  return n;
+}
 extern "C" int ofa_decode_steps(const ofa_ctx* c) { return c ? c->dec_steps_total : 0; }
 extern "C" int ofa_read_decode_tokens(ofa_ctx* c, int* out, size_t cap) {
   if (!c || !out || !c->h_out) return fail(c, OFA_BAD_ARGUMENT, "decode is not enabled");
@@ -1271,7 +1314,8 @@ extern "C" int ofa_run_phases(int dtype, const ofa_dims* dims, const ofa_phase* 
         break;
       case TK_CE: d.ntasks = (m.N + ew::CE_ROWS - 1) / ew::CE_ROWS;
         d.i0 = (int)(std::min<size_t>((size_t)((bf ? gemm_tc::BAR_OFFSET : smem - CTRL_BYTES) - 64), (size_t)m.V * (bf ? 2 : 4)) / 16 * 16); break;
-      case TK_CE_MEAN: case TK_BARRIER: d.ntasks = 1; break;
+      case TK_CE_MEAN: d.ntasks = 1; break;
+      case TK_BARRIER: d.ntasks = s.n > 0 ? (int)std::min<size_t>(s.n, 1u << 24) : 1; break;     // n empty tasks: what a task costs the scheduler alone
       case TK_EMB_WTE: d.ntasks = (m.V + ew::EMB_VCHUNK - 1) / ew::EMB_VCHUNK; break;
       case TK_EMB_WPE: d.ntasks = (m.T + ew::WPE_ROWS - 1) / ew::WPE_ROWS; break;
       case TK_ADAMW: d.ntasks = (int)((s.n + ew::OPT_CHUNK - 1) / ew::OPT_CHUNK); if (s.n == 0 || s.n % 4) { ar.free_all(); return fail(nullptr, OFA_BAD_ARGUMENT, "AdamW n must be a positive multiple of 4"); } break;

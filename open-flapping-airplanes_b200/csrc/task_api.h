@@ -76,12 +76,29 @@ struct Dep { int phase; int delta; };   // need done[phase] >= ntasks[phase] * (
 
 // Everything the scheduler thread needs to place a ticket in a phase and to check that phase's dependencies, in one 64-byte
 // line: one memory round trip per phase change instead of a chain of dependent table look-ups.
+//
+// Dependencies come in two grains. A phase-level dependency (the reference's only kind, ofa.cu:245-255) waits until EVERY task of
+// the producer phase has finished. A row-block dependency waits only for the producer tasks that write the 128-token row blocks
+// the waiting task reads: the producer counts its completions per row block as well (Job::done_rb), and the consumer derives the
+// row blocks it needs from its own task index (rb_map). Consecutive phases of the layer chain (LayerNorm -> GEMM -> attention ->
+// GEMM ...) then overlap instead of meeting at a barrier after every phase.
+enum RbKind : int {
+  RB_NONE = 0,
+  RB_MOD,        // task -> row block task % a            (GEMM strips: a = tiles along M, consecutive tasks walk down M)
+  RB_DIV,        // task -> row block task / a            (row-wise tasks: a = tasks per 128 rows)
+  RB_ATT_FWD,    // attention forward task (b, h, query tile): writes its query tile's row block, reads row blocks 0..tile of sequence b
+  RB_ATT_BWD,    // attention backward: dK/dV task (key tile) reads row blocks tile..last of its sequence; dQ task its own row block
+};
 struct alignas(16) SchedRec {
   int lo, hi;               // tickets [lo, hi) of a step belong to this phase
-  int ndeps;                // 0..4 dependencies held in dep[]; -1: more than four, use Job::deps
+  int ndeps;                // 0..4 dependencies held in dep[]; -1: more than four, use Job::deps (phase-level only)
   int perm_mul;             // 0 (production), or a multiplier coprime with the task count: ticket i of the phase runs task (i * perm_mul + perm_mul / 2) % ntasks (test hook: results must not depend on the order)
-  int dep[12];              // per dependency: phase, step delta, task count of that phase
+  int rb_off;               // where this phase counts completions per row block in Job::done_rb, -1: it does not
+  int rb_map;               // RbKind | a << 8
+  int dep[8];               // per dependency: {phase | (step delta == -1) << 16 | row-block grain << 17,  completions needed per step: tasks of the phase, or tasks per row block}
+  int pad[2];
 };
+constexpr int DEP_PREV = 1 << 16, DEP_RB = 1 << 17;
 constexpr int CTRL_BYTES = 1024;   // control area at the end of every block's dynamic shared memory
 // The scheduling records of both jobs travel with the launch as part of the kernel parameter (constant bank): a block that
 // claims a ticket finds the phase and its dependencies without a single round trip to global memory. Jobs with more phases than
@@ -98,6 +115,7 @@ struct Job {
   const Dep* deps;
   const SchedRec* rec;      // [nph]
   int* done;                // [nph] monotonically increasing over steps
+  int* done_rb;             // completions per (phase that publishes them, row block of 128 tokens), monotonically increasing; see SchedRec
   unsigned* ticket;         // next (step * tasks_per_step + task) to hand out
 };
 
@@ -164,6 +182,7 @@ struct Ctx {
   int* blk_info;            // per block: %smid | role << 16 (1 serve, 2 reserved-idle, 3 train, 4 idle)
   int* arrived;             // blocks of this launch that have started (idle partitions leave only when all have)
   int smem_bytes;           // dynamic shared memory per block; its last 1,024 bytes are the control area (barriers, hand-off words, descriptor slots)
+  int sched_flags;                          // bit 1: keep the per-phase / per-block time tables
   int train_rec_n, dec_rec_n;               // phases whose records are held below (0: use Job::rec in global memory)
   SchedRec train_rec[PARAM_TRAIN_PH];
   SchedRec dec_rec[PARAM_DEC_PH];

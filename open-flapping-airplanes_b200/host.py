@@ -199,6 +199,14 @@ class Megakernel:
             raise OfaError(capi.BAD_ARGUMENT, "no such phase")
         return [(ph[i], de[i]) for i in range(min(n, 64))]
 
+    def phase_dep_grain(self, phase):
+        """(rb_map of the phase, [1 if the dependency is waited for per 128-token row block else 0, ...] in phase_deps order)"""
+        rb = C.c_int(); gr = (C.c_int * 64)()
+        n = self.lib.ofa_phase_dep_grain(self.h, phase, C.byref(rb), gr, 64)
+        if n < 0:
+            raise OfaError(capi.BAD_ARGUMENT, "no such phase")
+        return rb.value, [gr[i] for i in range(min(n, 64))]
+
     # ---- decode
     @property
     def decode_steps(self):

@@ -33,7 +33,7 @@ GEMMS = {
     "gemm_dln1": (1, 0, M, D, 3 * D), "gemm_head_dX": (0, 0, M, D, V), "gemm_dWqkv": (2, 4, D, 3 * D, M), "gemm_dWo": (2, 4, D, D, M),
     "gemm_dWup": (2, 4, D, FF, M), "gemm_dWdown": (2, 4, FF, D, M), "gemm_head_dW": (2, 4, V, D, M),
 }
-OTHERS = ["attn_fwd", "attn_bwd", "adamw", "cross_entropy", "ln_fwd", "ln_bwd", "embed_bwd_wte", "decode_148sm", "decode_24sm", "decode_attn"]
+OTHERS = ["attn_fwd", "attn_bwd", "adamw", "cross_entropy", "ln_fwd", "ln_bwd", "embed_bwd_wte", "decode_148sm", "decode_24sm", "decode_attn", "sched_empty"]
 
 
 def peaks():
@@ -191,6 +191,18 @@ def run_decode(ofa, sms, ntok):
     return {"kernel": f"decode_{sms}sm", "shape": [sms], "ms": ms / ntok, "tok_s": ntok / ms * 1e3, "gbs": by / (ms / ntok) / 1e6, "bound": "hbm", "algorithmic_bytes": by}
 
 
+def run_sched_empty(ofa, repeats):
+    """What one task costs the scheduler when it does nothing: phases of empty tasks (64 per resident block and phase, two phases
+    chained) through the persistent kernel; time per task per block = claim + hand-off to the block + completion signal."""
+    K = ofa.capi
+    per_block, nblocks = 64, 296
+    phases = [ofa.phase(K.TK_BARRIER, n=per_block * nblocks), ofa.phase(K.TK_BARRIER, n=per_block * nblocks)]
+    ofa.run_phases(K.DTYPE_BF16, DIMS, phases, repeats=2)
+    ms = min(ofa.run_phases(K.DTYPE_BF16, DIMS, phases, repeats=max(5, repeats)) for _ in range(3)) / max(5, repeats)
+    us = ms * 1e3 / (2 * per_block)
+    return {"kernel": "sched_empty", "shape": [2, per_block * nblocks], "ms": ms, "us_per_task_per_block": us, "gbs": 0.0, "bound": "hbm", "note": "empty tasks: scheduler cost only"}
+
+
 def run_decode_attn(ofa, sms=148):
     """The serving job's attention task (one head's softmax attention over the KV cache + its slice of Wo; the reference's task_attwo,
     llm/b200/megakernel/decode_wide.cuh:321-428) at KV lengths 128 ... 1024: a decode-only context walks one context from position 0
@@ -257,6 +269,7 @@ def main():
         elif n == "decode_148sm": r = run_decode(ofa, 148, 261 * max(1, a.repeats))
         elif n == "decode_24sm": r = run_decode(ofa, 24, 261 * max(1, a.repeats))
         elif n == "decode_attn": r = run_decode_attn(ofa)
+        elif n == "sched_empty": r = run_sched_empty(ofa, a.repeats)
         else: raise SystemExit(f"unknown case {n}")
         for rec in (r if isinstance(r, list) else [r]):
             rec["frac"] = (rec["tflops"] / tf) if rec["bound"] == "tensor" else (rec["gbs"] / hbm)

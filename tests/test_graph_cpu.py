@@ -132,3 +132,36 @@ def test_trickled_adamw_covers_every_parameter_once(ofa):
             assert tr.phase_deps(i) == [(ready, 0)]
     assert "adamw L0 .0" not in names and "adamw L0" in names             # nothing left to spread the last group into
     base.close(); tr.close()
+
+
+def test_row_block_dependencies_follow_the_layer_chain(ofa):
+    """On the tensor-core path the layer chain waits per 128-token row block: LayerNorm -> GEMM -> attention -> GEMM ... Every such
+    edge must join two phases whose tasks map to row blocks, stay inside one step, and the producers must have a whole number of
+    tasks per row block; reductions over all tokens (weight-gradient GEMMs, dgamma, embedding backward, AdamW) keep the phase grain.
+    The fp32 preset (row counts that are not multiples of 128) keeps the phase grain everywhere."""
+    mk = plan(ofa, "gpt_s")
+    ph = mk.phases(); names = [p["name"] for p in ph]
+    nrb = 4 * 1024 // 128
+    fine = {}
+    for i, p in enumerate(ph):
+        rb_map, grain = mk.phase_dep_grain(i)
+        deps = mk.phase_deps(i)
+        for (d, delta), g in zip(deps, grain):
+            if g:
+                assert delta == 0 and rb_map != 0 and mk.phase_dep_grain(d)[0] != 0
+                assert ph[d]["ntasks"] % nrb == 0, names[d]
+                fine[(names[d], p["name"])] = True
+    for l in (0, 5, 11):
+        for a, b in [("ln1", "qkv"), ("qkv", "attn"), ("attn", "wo+res"), ("wo+res", "ln2"), ("ln2", "up+gelu"), ("up+gelu", "down+res"),
+                     ("dpre", "dln2"), ("dln2", "ln2 bwd"), ("ln2 bwd", "dO"), ("dO", "attn bwd"), ("attn bwd", "dln1"), ("dln1", "ln1 bwd")]:
+            assert (f"L{l} {a}", f"L{l} {b}") in fine, (l, a, b)
+    for a, b in [("embed", "L0 ln1"), ("L3 down+res", "L4 ln1"), ("L11 down+res", "lnf"), ("lnf", "logits"), ("logits", "cross-entropy"),
+                 ("cross-entropy", "head dX"), ("head dX", "lnf bwd"), ("lnf bwd", "L11 dpre"), ("L4 ln1 bwd", "L3 dpre")]:
+        assert (a, b) in fine, (a, b)
+    coarse = lambda name: all(g == 0 for g in mk.phase_dep_grain(names.index(name))[1])
+    for name in ["head dW", "L7 dWdown", "L7 dWup", "L7 dWo", "L7 dWqkv", "L7 dgamma1", "L7 dgamma2", "embed bwd wte", "embed bwd wpe", "adamw L7", "adamw head", "loss mean", "step barrier"]:
+        assert coarse(name), name
+    mk.close()
+    tiny = plan(ofa, "tiny")
+    assert all(not any(tiny.phase_dep_grain(i)[1]) for i in range(len(tiny.phases())))
+    tiny.close()
