@@ -155,7 +155,8 @@ enum {  /* task kinds, = TaskKind of the device code */
 };
 enum { OFA_GEMM_NN = 0, OFA_GEMM_NT = 1, OFA_GEMM_TN = 2 };
 enum { OFA_EPI_STORE = 0, OFA_EPI_RES = 1, OFA_EPI_GELU = 2, OFA_EPI_DGELU = 3, OFA_EPI_F32 = 4,
-       OFA_EPI_DR = 5 /* C = acc and p[4][b,h,t] = sum over head h's columns of C * aux: attention backward's row term fused into the GEMM that produces dO */ };
+       OFA_EPI_DR = 5 /* C = acc and p[4][b,h,t] = sum over head h's columns of C * aux: attention backward's row term fused into the GEMM that produces dO */,
+       OFA_EPI_LSE = 6 /* C = acc and p[4][row][N/128] = float2 {max, sum of exponentials} of each 128-column tile of the stored row, in the log2 domain: softmax partials of the LM head (NT layout); an OFA_TK_CE phase given them as its p[3] reads the logits once instead of twice (the reference's cross-entropy makes two passes, llm/elementwise/ew_loss.cuh:19-75) */ };
 
 /* One phase = ntasks independent block-sized tasks (PhaseDesc, ofa.cu:89-95). Pointers are DEVICE pointers obtained
  * from ofa_dev_alloc. For GEMM phases ntasks/tiles are derived from M,N,K and the TMA descriptors are built here. */

@@ -102,7 +102,7 @@ MODE_TRAIN, MODE_FORWARD, MODE_NO_OPT, MODE_DECODE_ONLY = 0, 1, 2, 3
 (TK_DATA, TK_EMBED, TK_LN_FWD, TK_GEMM, TK_ATT_FWD, TK_ATT_PREP, TK_ATT_BWD, TK_CE, TK_CE_MEAN, TK_LN_BWD, TK_LN_DG, TK_EMB_WTE,
  TK_EMB_WPE, TK_ADAMW, TK_BARRIER) = range(15)
 GEMM_NN, GEMM_NT, GEMM_TN = 0, 1, 2
-EPI_STORE, EPI_RES, EPI_GELU, EPI_DGELU, EPI_F32, EPI_DR = range(6)
+EPI_STORE, EPI_RES, EPI_GELU, EPI_DGELU, EPI_F32, EPI_DR, EPI_LSE = range(7)
 OUT_RESTART = 1 << 24
 OUT_FORCED = OUT_RESTART + 1
 

@@ -130,6 +130,9 @@ template <bool FAST> __device__ __forceinline__ float gelu_bwd(float x) {
   return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * du;
 }
 
+// 2^x on the special-function unit (results below 2^-126 flush to zero; 2^-inf = 0)
+__device__ __forceinline__ float ex2_approx(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+
 __device__ __forceinline__ u64 splitmix64(u64 z) {
   z += 0x9E3779B97F4A7C15ull;
   z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;

@@ -24,6 +24,10 @@ constexpr int OPT_CHUNK = 65536;     // elements per AdamW task
 constexpr int WPE_ROWS = 4;          // positions per wpe-backward task
 constexpr int SUM_CHUNK = 16384;     // elements per split-K reduce task
 
+// global -> shared bulk copy by the copy engine (16-byte aligned addresses, size a multiple of 16), completion counted in bytes on `bar`
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
 __device__ __forceinline__ void ld4(const float* p, float* f) { ldv(p, f); }
 __device__ __forceinline__ void ld4(const bf16* p, float* f) {
   const uint2 u = *reinterpret_cast<const uint2*>(p);
@@ -333,6 +337,92 @@ __device__ __forceinline__ void ce_task_bulk(int task, bf16* logits, const int* 
   }
 }
 
+// Cross-entropy behind an LM-head GEMM whose epilogue left softmax partials (GE_LSE): per row and 128-column tile the maximum m_t
+// of x * log2(e) over the stored values and s_t = sum 2^(x * log2(e) - m_t). The row's maximum and sum follow from the tiles_n
+// partials (a few KB) without touching the logits, so the logits are read ONCE and rewritten in the same pass:
+//   M = max_t m_t,  S = sum_t s_t * 2^(m_t - M)  (fixed order),  loss = M * ln2 + ln S - logit[target],
+//   dlogit = (2^(x * log2(e) - M) / S - onehot) * inv_n.
+// The task's rows move through shared memory as one stream of chunks staged by the copy engine, four chunks (96 KB) in flight
+// across row boundaries; nothing waits for a whole row. `bar_lo`, `bar_hi` = two pairs of block-private mbarriers (count 1), `chunks` = running
+// count of chunks this block has staged (advanced identically by every thread). V must be a multiple of 8.
+constexpr int CE_CHUNK = 12288, CE_STAGES = 4;            // elements per chunk (24 KB of bf16)
+__device__ __forceinline__ void ce_task_stream(int task, bf16* logits, const int* targets, float* loss, const float2* part, int tiles_n,
+                                               int N, int V, float inv_n, unsigned char* smem, uint32_t bar_lo, uint32_t bar_hi, uint32_t& chunks,
+                                               const DevStatus* st) {
+  auto sbar = [&](uint32_t sg) { return sg < 2 ? bar_lo + 8u * sg : bar_hi + 8u * (sg - 2); };   // the four barriers sit in two free pairs of the control area
+  constexpr float L2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
+  float* rowMS = reinterpret_cast<float*>(smem + CE_STAGES * CE_CHUNK * 2);        // [CE_ROWS][2] behind the stages: M and 1/S of the task's rows
+  const int t = threadIdx.x;
+  const int r0 = task * CE_ROWS, nrows = min(CE_ROWS, N - r0);
+  const int cpr = (V + CE_CHUNK - 1) / CE_CHUNK;                                   // chunks per row
+  const int total = nrows > 0 ? nrows * cpr : 0;
+  const uint32_t u0 = chunks;
+  chunks += (uint32_t)total;                                                       // every thread, whatever happens below
+  const uint32_t sbase = smem_u32(smem);
+  auto issue = [&](int k) {                                                        // thread 0: chunk k of this task into stage (u0 + k) % 4
+    const uint32_t u = u0 + (uint32_t)k, sg = u % CE_STAGES, b = sbar(sg);
+    const int rr = k / cpr, c0 = (k % cpr) * CE_CHUNK;
+    const uint32_t bytes = (uint32_t)min(CE_CHUNK, V - c0) * 2u;
+    mbar_expect_tx(b, bytes);
+    bulk_g2s(sbase + sg * (CE_CHUNK * 2), logits + (size_t)(r0 + rr) * V + c0, bytes, b);
+  };
+  if (t == 0 && total > 0) {
+    fence_proxy_async();     // the rows were written by a GEMM epilogue with ordinary stores; the stages were last read by ordinary loads
+    for (int k = 0; k < CE_STAGES && k < total; k++) issue(k);
+  }
+  // row statistics from the partials while the first chunks travel: one warp per row, lanes over the tiles, fixed reduction order
+  {
+    const int warp = t >> 5, lane = t & 31;
+    if (warp < nrows) {
+      const int rr = warp;
+      const float2* pr = part + (size_t)(r0 + rr) * tiles_n;
+      float m = -INFINITY;
+      for (int i = lane; i < tiles_n; i += 32) m = fmaxf(m, pr[i].x);
+      const float M = warp_max(m);
+      float sm = 0.f;
+      for (int i = lane; i < tiles_n; i += 32) { const float2 v = pr[i]; sm += v.y * exp2f(v.x - M); }
+      const float S = warp_sum(sm);
+      if (lane == 0) {
+        rowMS[2 * rr] = M; rowMS[2 * rr + 1] = 1.f / S;
+        loss[r0 + rr] = M * LN2 + logf(S) - to_f(logits[(size_t)(r0 + rr) * V + targets[r0 + rr]]);   // read before the row's chunks are rewritten (ordered by the barrier below)
+      }
+    }
+  }
+  __syncthreads();
+  for (int k = 0; k < total; k++) {
+    const uint32_t u = u0 + (uint32_t)k, sg = u % CE_STAGES;
+    const bool ok = mbar_wait(sbar(sg), (u / CE_STAGES) & 1u, st);
+    if (ok) {
+      const int rr = k / cpr, c0 = (k % cpr) * CE_CHUNK, len = min(CE_CHUNK, V - c0);
+      const float M = rowMS[2 * rr], scale = rowMS[2 * rr + 1] * inv_n;             // p * inv_n = 2^(x log2e - M) * (inv_n / S)
+      const int tgt = targets[r0 + rr] - c0;                                       // position of the target inside this chunk, if it is there
+      const bf16* src = reinterpret_cast<const bf16*>(smem + sg * (CE_CHUNK * 2));
+      bf16* dst = logits + (size_t)(r0 + rr) * V + c0;
+      for (int v = t * 8; v < len; v += NTHR * 8) {
+        float f[8];
+        unpack8(*reinterpret_cast<const uint4*>(src + v), f);
+#pragma unroll
+        for (int i = 0; i < 8; i++) f[i] = ex2_approx(fmaf(f[i], L2E, -M)) * scale;
+        if ((unsigned)(tgt - v) < 8u) {                                             // the one-hot term: (p - 1) * inv_n (no dynamic register index)
+#pragma unroll
+          for (int i = 0; i < 8; i++) if (tgt - v == i) f[i] -= inv_n;
+        }
+        *reinterpret_cast<uint4*>(dst + v) = pack8(f);
+      }
+    }
+    if (__syncthreads_or(!ok)) {                        // giving up (abort or deadline): let the copies still in flight land, then leave
+      if (t == 0)
+        for (int kk = k; kk < total && kk < k + CE_STAGES; kk++) {
+          const uint32_t uu = u0 + (uint32_t)kk;
+          for (int spin = 0; spin < 100000 && !mbar_try(sbar(uu % CE_STAGES), (uu / CE_STAGES) & 1u); spin++) {}
+        }
+      __syncthreads();
+      return;
+    }
+    if (t == 0 && k + CE_STAGES < total) { fence_proxy_async(); issue(k + CE_STAGES); }
+  }
+}
+
 // mean_loss[0] = (sum_r loss[r]) / N, fixed order. One task.
 __device__ __forceinline__ float ce_mean_task(float* mean_loss, const float* loss, int N, unsigned char* smem) {
   float s = 0.f;
@@ -498,9 +588,6 @@ __device__ __forceinline__ void adamw_task(int task, float* W, const GT* G, floa
 // `tiles` = running count of tiles this block has staged since it started (advanced identically by every thread).
 // The ragged end of a range (fewer than 2,048 elements, or byte counts that are not multiples of 16) goes through the loop above.
 constexpr int ADAM_TILE = 2048, ADAM_STAGES = 3, ADAM_STAGE_BYTES = 32768;
-__device__ __forceinline__ void adam_bulk(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
 template <class T, class GT>
 __device__ __forceinline__ void adamw_task_bulk(int task, float* W, const GT* G, float* M, float* Vv, T* Wact, size_t n, AdamHP hp,
                                                 const int2* nodecay, int n_nodecay, unsigned char* smem, uint32_t bar0, uint32_t& tiles,
@@ -549,8 +636,8 @@ __device__ __forceinline__ void adamw_task_bulk(int task, float* W, const GT* G,
     const uint32_t u = u0 + (uint32_t)k, s = u % ADAM_STAGES, b = bar0 + 8u * s, dst = sbase + s * ADAM_STAGE_BYTES;
     const size_t i0 = cs + (size_t)k * ADAM_TILE;
     mbar_expect_tx(b, 3u * ADAM_TILE * 4u + (uint32_t)(ADAM_TILE * sizeof(GT)));
-    adam_bulk(dst, W + i0, ADAM_TILE * 4, b); adam_bulk(dst + 8192, M + i0, ADAM_TILE * 4, b);
-    adam_bulk(dst + 16384, Vv + i0, ADAM_TILE * 4, b); adam_bulk(dst + 24576, G + i0, (uint32_t)(ADAM_TILE * sizeof(GT)), b);
+    bulk_g2s(dst, W + i0, ADAM_TILE * 4, b); bulk_g2s(dst + 8192, M + i0, ADAM_TILE * 4, b);
+    bulk_g2s(dst + 16384, Vv + i0, ADAM_TILE * 4, b); bulk_g2s(dst + 24576, G + i0, (uint32_t)(ADAM_TILE * sizeof(GT)), b);
   };
   if (tid == 0 && nfull > 0) {
     fence_proxy_async();     // gradients and the previous step's W/M/V were written with ordinary stores; the stages were last read by ordinary loads

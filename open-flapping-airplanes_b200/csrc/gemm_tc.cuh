@@ -53,6 +53,7 @@ template <int BN> struct Cfg {
 };
 // control area (1 KB at smem + BAR_OFFSET = the last 1,024 bytes of dynamic shared memory):
 //   [  0, 80) BN128: full[3] empty[3] accf[2] acce[2]     [ 80, 84) TMEM base slot     [ 96,104) serving fill barrier   [104,112) training bulk-copy barrier
+//   [112,128) and [160,176) streamed cross-entropy stage barriers [4]
 //   [128,160) scheduler hand-off words                      [176,224) BN256: full[2] empty[2] accf[1] acce[1]      [224,248) AdamW stage barriers [3]
 //   [256,512) and [512,768) two slots for phase descriptors: the one being worked on and the next phase's, fetched ahead
 //   [768,832) scheduling record (ticket range + dependencies) of the phase the scheduler thread looks at next
@@ -250,6 +251,10 @@ __device__ __forceinline__ void gemm_tc_task(const GemmArgs& g, int tiles_m, int
           if (!ok) break;
           tc_fence_after();
         }
+        // GE_LSE: running maximum (log2 domain) and sum of 2^(x - max) of this lane's share of four rows, over the tile's 128 columns
+        float lm[EPI == GE_LSE ? 4 : 1], ls[EPI == GE_LSE ? 4 : 1];
+#pragma unroll
+        for (int i = 0; i < (EPI == GE_LSE ? 4 : 1); i++) { lm[i] = -INFINITY; ls[i] = 0.f; }
         float drp[EPI == GE_DR ? 8 : 1];                 // GE_DR: this lane's partial row sums, [row slot it][head of the tile]
 #pragma unroll
         for (int i = 0; i < (EPI == GE_DR ? 8 : 1); i++) drp[i] = 0.f;
@@ -275,10 +280,40 @@ __device__ __forceinline__ void gemm_tc_task(const GemmArgs& g, int tiles_m, int
             const float4 a0 = *reinterpret_cast<const float4*>(stg + rr * 32 + (((2 * cg) ^ (rr & 7)) << 2));
             const float4 a1 = *reinterpret_cast<const float4*>(stg + rr * 32 + (((2 * cg + 1) ^ (rr & 7)) << 2));
             const float acc[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-            const float part = epi_store8<EPI>(g, (size_t)(m0 + e * 32 + rr), n0 + half * 128 + c * 32 + cg * 8, acc, auxr[HAS_AUX_IN ? c * 4 + it : 0]);
-            if constexpr (EPI == GE_DR) drp[it * 2 + (c >> 1)] += part;
+            if constexpr (EPI == GE_LSE) {
+              const uint4 out = pack8(acc);
+              *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(g.C) + (size_t)(m0 + e * 32 + rr) * g.ldc + n0 + half * 128 + c * 32 + cg * 8) = out;
+              float y[8]; unpack8(out, y);             // the STORED values: the partials describe exactly what cross-entropy will read
+              float gm = y[0];
+#pragma unroll
+              for (int i = 1; i < 8; i++) gm = fmaxf(gm, y[i]);
+              gm *= 1.4426950408889634f;
+              if (gm > lm[it]) { ls[it] *= ex2_approx(lm[it] - gm); lm[it] = gm; }
+              float s2 = 0.f;
+#pragma unroll
+              for (int i = 0; i < 8; i += 2) { ls[it] += ex2_approx(fmaf(y[i], 1.4426950408889634f, -lm[it])); s2 += ex2_approx(fmaf(y[i + 1], 1.4426950408889634f, -lm[it])); }
+              ls[it] += s2;
+            } else {
+              const float part = epi_store8<EPI>(g, (size_t)(m0 + e * 32 + rr), n0 + half * 128 + c * 32 + cg * 8, acc, auxr[HAS_AUX_IN ? c * 4 + it : 0]);
+              if constexpr (EPI == GE_DR) drp[it * 2 + (c >> 1)] += part;
+            }
           }
           __syncwarp();
+        }
+        if constexpr (EPI == GE_LSE) {                   // a row's 128 columns sit in the 4 lanes of a quad: merge their (max, sum) pairs, same result in all four
+          float2* part = reinterpret_cast<float2*>(g.dr) + (size_t)(m0 + e * 32 + (lane >> 2)) * (g.N / 128) + (n0 + half * 128) / 128;
+#pragma unroll
+          for (int it = 0; it < 4; it++) {
+            float m_ = lm[it], s_ = ls[it];
+#pragma unroll
+            for (int o = 1; o <= 2; o <<= 1) {
+              const float mo = __shfl_xor_sync(0xffffffffu, m_, o), so = __shfl_xor_sync(0xffffffffu, s_, o);
+              const float mn = fmaxf(m_, mo);
+              s_ = s_ * ex2_approx(m_ - mn) + so * ex2_approx(mo - mn);
+              m_ = mn;
+            }
+            if (cg == 0) part[(size_t)it * 8 * (g.N / 128)] = make_float2(m_, s_);
+          }
         }
         if constexpr (EPI == GE_DR) {                    // a row's 64 columns of a head sit in the 4 lanes of a quad (2 chunks each)
           // the 128 rows of a tile belong to one sequence (the context length is a multiple of 128): one division per tile
@@ -314,6 +349,7 @@ __device__ __noinline__ void run(const PhaseDesc& d, int task, unsigned char* sm
     case GL_NT * 8 + GE_STORE: dispatch_bn<GL_NT, GE_STORE>(d, task, smem, gp, st, phase_id); break;
     case GL_NT * 8 + GE_DGELU: dispatch_bn<GL_NT, GE_DGELU>(d, task, smem, gp, st, phase_id); break;
     case GL_NT * 8 + GE_DR:    gemm_tc_task<GL_NT, GE_DR, 128>(d.g, d.tiles_m, task, smem, gp, st, phase_id); break;
+    case GL_NT * 8 + GE_LSE:   gemm_tc_task<GL_NT, GE_LSE, 128>(d.g, d.tiles_m, task, smem, gp, st, phase_id); break;
     case GL_TN * 8 + GE_F32:   dispatch_bn<GL_TN, GE_F32>(d, task, smem, gp, st, phase_id); break;
     case GL_TN * 8 + GE_STORE: dispatch_bn<GL_TN, GE_STORE>(d, task, smem, gp, st, phase_id); break;
     default: if (threadIdx.x == 0) raise_abort(st, ST_BAD_DESC, phase_id, task, d.layout * 8 + d.epi); __syncthreads(); break;

@@ -31,7 +31,7 @@ template <class T> struct IsBf16 { static constexpr bool value = std::is_same<T,
 // ---------------------------------------------------------------------------------------------- one training task
 template <class T, int D, int DH>
 __device__ __forceinline__ void run_train_task(const Ctx& C, const PhaseDesc& d, int ph, int local, int step, unsigned char* smem,
-                                               gemm_tc::GemmPipe& gp, attn_tc::AttnPipe& ap, uint32_t& bulk_uses, uint32_t& adam_tiles) {
+                                               gemm_tc::GemmPipe& gp, attn_tc::AttnPipe& ap, uint32_t& bulk_uses, uint32_t& adam_tiles, uint32_t& ce_chunks) {
   const ModelDims& md = C.md;
   switch (d.kind) {
     case TK_DATA:
@@ -88,6 +88,11 @@ __device__ __forceinline__ void run_train_task(const Ctx& C, const PhaseDesc& d,
     }
     case TK_CE:
       if constexpr (IsBf16<T>::value) {
+        if (d.p[3] && md.V % 8 == 0) {                 // the LM-head GEMM left softmax partials: one streamed pass over the logits
+          ew::ce_task_stream(local, (bf16*)d.p[0], (const int*)d.p[1], (float*)d.p[2], (const float2*)d.p[3], d.i2, md.N, md.V, 1.0f / (float)md.N, smem,
+                             smem_u32(smem + C.smem_bytes - CTRL_BYTES + 112), smem_u32(smem + C.smem_bytes - CTRL_BYTES + 160), ce_chunks, C.status);
+          break;
+        }
         if ((size_t)md.V * 2 <= (size_t)d.i0 && md.V % 8 == 0) {
           ew::ce_task_bulk(local, (bf16*)d.p[0], (const int*)d.p[1], (float*)d.p[2], md.N, md.V, 1.0f / (float)md.N, smem,
                            smem_u32(smem + C.smem_bytes - CTRL_BYTES + 104), bulk_uses, C.status);
@@ -289,8 +294,13 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
   attn_tc::AttnPipe ap; ap.tasks = ap.stages = ap.stages2 = ap.a = ap.b = ap.done = 0;
   uint32_t bulk_uses = 0;                            // uses of the block's bulk-copy barrier (control area byte 104)
   uint32_t adam_tiles = 0;                           // tiles the block's AdamW tasks have staged (three barriers at control area byte 224)
+  uint32_t ce_chunks = 0;                            // chunks the block's streamed cross-entropy tasks have staged (barriers at bytes 112, 120, 160, 168)
   if (use_tc) {
-    if (tid == 0) { mbar_init(smem_u32(ctrl + 104), 1); for (int q = 0; q < ew::ADAM_STAGES; q++) mbar_init(smem_u32(ctrl + 224 + 8 * q), 1); }
+    if (tid == 0) {
+      mbar_init(smem_u32(ctrl + 104), 1);
+      for (int q = 0; q < ew::ADAM_STAGES; q++) mbar_init(smem_u32(ctrl + 224 + 8 * q), 1);
+      for (int q = 0; q < 2; q++) { mbar_init(smem_u32(ctrl + 112 + 8 * q), 1); mbar_init(smem_u32(ctrl + 160 + 8 * q), 1); }   // streamed cross-entropy: four stages
+    }
     attn_tc::block_init(ap, smem); gemm_tc::block_init(gp, smem, C.status);
   }
   // serving blocks: one mbarrier counts the bytes of the weight prefetch of the task they hold a ticket for
@@ -409,7 +419,7 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
     if (tid == 0) {
       if (prof) { t0 = gtimer(); t_sync += t0 - tl1; if (job_id == 1 && C.dp.trace && local == 0 && (ph == 0 || ph == 2)) C.dp.trace[16 + ph] = t0; }
     }
-    if (job_id == 0) run_train_task<T, D, DH>(C, d, ph, local, step, smem, gp, ap, bulk_uses, adam_tiles);
+    if (job_id == 0) run_train_task<T, D, DH>(C, d, ph, local, step, smem, gp, ap, bulk_uses, adam_tiles, ce_chunks);
     else run_decode_task<T, D, DH>(C, d, local, smem, fill_bar, fills & 1u);
     if (filled) fills++;
     __syncthreads();

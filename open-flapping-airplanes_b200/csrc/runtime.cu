@@ -137,12 +137,13 @@ bool prepare_gemm_bf16(PhaseDesc& d, Arena& ar, int nsub_cfg, int nblocks, std::
     return false;
   }
   if ((d.epi == GE_RES || d.epi == GE_GELU || d.epi == GE_DGELU || d.epi == GE_DR) && !g.aux) { err = "GEMM epilogue needs aux"; return false; }
+  if (d.epi == GE_LSE && (d.layout != GL_NT || !g.dr)) { err = "softmax-partial epilogue: NT layout with an output for the partials"; return false; }
   // nsub_cfg: n = strips of n tiles (0 = automatic); 2000 + n = the same with 256-wide tiles where N allows. 256-wide tiles are
   // opt-in: with two 48 KB stages per block they measured slower than three 32 KB stages of the 128-wide tile on every model
   // shape except lm_head dW (960 vs 702 TFLOP/s), i.e. the main loop is bound by bytes in flight, not by operand traffic alone.
   const bool want256 = nsub_cfg >= 2000;
   if (want256) nsub_cfg -= 2000;
-  g.bn = (want256 && g.N % 256 == 0 && d.epi != GE_DR) ? 256 : 128;
+  g.bn = (want256 && g.N % 256 == 0 && d.epi != GE_DR && d.epi != GE_LSE) ? 256 : 128;
   const int tm = g.M / 128, tn = g.N / g.bn;
   int nsub = nsub_cfg;
   if (nsub <= 0) {
@@ -455,12 +456,25 @@ bool build_train_graph(ofa_ctx* c) {
   }
   { PhaseDesc d = mk(TK_LN_FWD, rows16); d.p[0] = lnf; d.p[1] = meanf; d.p[2] = rstdf; d.p[3] = xs[L]; d.p[4] = Wact + lay.gf;
     addp("lnf", d, {prev}, {fwd_only ? "" : "head dW"}, {prev}); }
-  addp("logits", mkgemm(GL_NT, GE_STORE, lnf, D, Wact + lay.head, D, logits, V, nullptr, 0, N, V, D, 0), {"lnf"}, {opt_head}, {"lnf"});
+  // Head fusion: with a backward pass behind it the LM-head GEMM also leaves, per row and 128-column tile, the maximum and the sum
+  // of exponentials of the values it stored; cross-entropy then reads the logits once instead of twice (the reference reads them
+  // in two passes, llm/elementwise/ew_loss.cuh:19-75).
+  float2* lse_part = nullptr;
+  const bool fuse_head = bf && !fwd_only && V % 128 == 0 && !getenv("OFA_B200_CE_TWO_PASS");     // the switch keeps the two-pass task for A/B measurements
+  if (fuse_head) lse_part = reinterpret_cast<float2*>(abuf<float>(c, "lse_part", N * (V / 128) * 2));
+  {
+    PhaseDesc d = mk(TK_GEMM, 0); d.layout = GL_NT; d.epi = fuse_head ? GE_LSE : GE_STORE;
+    d.g.A = lnf; d.g.B = Wact + lay.head; d.g.C = logits; d.g.aux = nullptr; d.g.M = (int)N; d.g.N = (int)V; d.g.K = (int)D; d.g.lda = (int)D; d.g.ldb = (int)D; d.g.ldc = (int)V;
+    d.g.dr = reinterpret_cast<float*>(lse_part);
+    if (bf) { std::string e; if (!prepare_gemm_bf16(d, c->ar, cfg.gemm_nsub, c->C.train_sms > 0 ? 2 * c->C.train_sms : c->nblocks, e)) { ok = false; err = e; } }
+    else prepare_gemm_f32(d);
+    addp("logits", d, {"lnf"}, {opt_head}, {"lnf"});
+  }
   std::vector<std::string> end_deps;
   if (fwd_only) {
     end_deps = {"logits"};
   } else {
-    { PhaseDesc d = mk(TK_CE, (int)((N + ew::CE_ROWS - 1) / ew::CE_ROWS)); d.p[0] = logits; d.p[1] = c->C.tok_tgt; d.p[2] = lossv;
+    { PhaseDesc d = mk(TK_CE, (int)((N + ew::CE_ROWS - 1) / ew::CE_ROWS)); d.p[0] = logits; d.p[1] = c->C.tok_tgt; d.p[2] = lossv; d.p[3] = lse_part; d.i2 = (int)(V / 128);
       const size_t usable = (size_t)((bf ? gemm_tc::BAR_OFFSET : c->smem - CTRL_BYTES) - 64);
       d.i0 = (int)(std::min(usable, V * sizeof(T)) / 16 * 16);
       addp("cross-entropy", d, {"logits", "data"}, {}, {"logits"}); }
@@ -1296,6 +1310,10 @@ extern "C" int ofa_run_phases(int dtype, const ofa_dims* dims, const ofa_phase* 
       case TK_GEMM:
         d.g.A = s.p[0]; d.g.B = s.p[1]; d.g.C = s.p[2]; d.g.aux = s.p[3]; d.g.M = s.M; d.g.N = s.N; d.g.K = s.K; d.g.lda = s.lda; d.g.ldb = s.ldb; d.g.ldc = s.ldc; d.g.ldaux = s.ldaux;
         d.g.accumulate = s.accumulate;
+        if (s.epi == GE_LSE) {  // p[4] = softmax partials [M, N / 128] float2
+          if (!bf || !s.p[4] || s.layout != GL_NT) { ar.free_all(); return fail(nullptr, OFA_BAD_ARGUMENT, "softmax-partial epilogue: bf16, NT layout, p[4] = output [M, N/128] float2"); }
+          d.g.dr = reinterpret_cast<float*>(s.p[4]);
+        }
         if (s.epi == GE_DR) {   // p[4] = row-term output [B, H, T]; needs the tensor-core path, heads of 64 columns and whole rows of heads in C
           if (!bf || !s.p[4] || s.layout != GL_NT || s.N != m.D || s.M != m.N) { ar.free_all(); return fail(nullptr, OFA_BAD_ARGUMENT, "row-term epilogue: bf16, NT layout, C = [tokens, d_model], p[4] = output"); }
           d.g.dr = reinterpret_cast<float*>(s.p[4]); d.g.dr_T = m.T; d.g.dr_H = m.H;
@@ -1313,6 +1331,7 @@ extern "C" int ofa_run_phases(int dtype, const ofa_dims* dims, const ofa_phase* 
         if (bf && !s.i0) { d.p[6] = const_cast<void*>(make_attn_maps(ar, s.p[0], s.p[1], m.N, m.D, err)); if (!d.p[6]) { ar.free_all(); return fail(nullptr, OFA_CUDA_ERROR, err); } }
         break;
       case TK_CE: d.ntasks = (m.N + ew::CE_ROWS - 1) / ew::CE_ROWS;
+        if (s.p[3]) { if (!bf || m.V % 128) { ar.free_all(); return fail(nullptr, OFA_BAD_ARGUMENT, "cross-entropy with softmax partials: bf16, vocab a multiple of 128"); } d.i2 = m.V / 128; }
         d.i0 = (int)(std::min<size_t>((size_t)((bf ? gemm_tc::BAR_OFFSET : smem - CTRL_BYTES) - 64), (size_t)m.V * (bf ? 2 : 4)) / 16 * 16); break;
       case TK_CE_MEAN: d.ntasks = 1; break;
       case TK_BARRIER: d.ntasks = s.n > 0 ? (int)std::min<size_t>(s.n, 1u << 24) : 1; break;     // n empty tasks: what a task costs the scheduler alone

@@ -49,6 +49,9 @@ enum GemmEpi : int {
   GE_F32,         // C(fp32) = acc, or C += acc when `accumulate`
   GE_DR,          // C = act(acc); dr[b, h, t] = sum over head h's 64 columns of float(C) * aux   (attention backward's row term,
                   // with C = dO and aux = O; tensor-core path only)
+  GE_LSE,         // C = act(acc); lse_part[row, tile_n] = {m, s}: m = max over the tile's 128 stored (rounded) values of x * log2(e),
+                  // s = sum of 2^(x * log2(e) - m)   (softmax partials of the LM head: cross-entropy then needs one pass over the
+                  // logits instead of two; tensor-core path only)
 };
 
 struct GemmArgs {
@@ -60,7 +63,7 @@ struct GemmArgs {
   int bn;                     // tile width of the tensor-core path: 256 when N is a multiple of 256, else 128
   const void* tmA;            // device pointers to the two TMA descriptors (tensor-core path), 64-byte aligned
   const void* tmB;
-  float* dr; int dr_T, dr_H;  // GE_DR only: output [B, H, T] and its dimensions (row = b * T + t, head = column / 64)
+  float* dr; int dr_T, dr_H;  // GE_DR: output [B, H, T] and its dimensions (row = b * T + t, head = column / 64). GE_LSE: dr = output [M, N / 128] float2
 };
 
 struct alignas(16) PhaseDesc {

@@ -121,6 +121,46 @@ def test_cross_entropy(ofa, K, bf, V):
     assert relmax(d_lg.download(), lgr.grad) <= (2e-2 if bf else 1e-5)
 
 
+@pytest.mark.parametrize("V,N", [(1024, 256), (50304, 128), (1152, 384)])
+def test_fused_head_softmax_partials_and_one_pass_cross_entropy(ofa, K, V, N):
+    """The LM-head GEMM with the epilogue that leaves per-tile softmax partials, followed by the cross-entropy task that reads the
+    logits once: the partials must reproduce each row's logsumexp of the STORED (bf16) logits, and loss / dlogits must equal
+    F.cross_entropy on those stored logits at the tolerances of the two-pass task. Peaked rows as in ref_elementwise.py:24-26."""
+    D = 768
+    dims = dict(DIMS_S, vocab=V, ctx_len=128, batch=N // 128)
+    g = torch.Generator().manual_seed(21)
+    x = rnd(torch.randn(N, D, generator=g), True); W = rnd(torch.randn(V, D, generator=g) * 0.1, True)
+    tg = torch.randint(0, V, (N,), generator=g, dtype=torch.int32)
+    W[tg[:8].long()] *= 4                                              # a few very peaked rows
+    W = rnd(W, True)
+    d_x = ofa.DeviceBuffer.from_host(x.numpy(), "bf16"); d_W = ofa.DeviceBuffer.from_host(W.numpy(), "bf16"); d_tg = ofa.DeviceBuffer.from_host(tg.numpy(), np.int32)
+    d_lg = ofa.DeviceBuffer((N, V), "bf16"); d_part = ofa.DeviceBuffer((N, V // 128, 2), np.float32)
+    ph = ofa.gemm_phase(1, K.EPI_LSE, N, V, D, d_x, D, d_W, D, d_lg, V, nsub=3)
+    ph.p[4] = d_part.ptr
+    ofa.run_phases(K.DTYPE_BF16, dims, [ph])
+    stored = torch.from_numpy(d_lg.download())
+    assert relmax(stored, (x.double() @ W.double().T).float()) <= 2e-2
+    part = d_part.download().astype(np.float64)                         # log2 domain
+    M = part[:, :, 0].max(1); S = (part[:, :, 1] * np.exp2(part[:, :, 0] - M[:, None])).sum(1)
+    lse = M * np.log(2.0) + np.log(S)
+    assert np.abs(lse - torch.logsumexp(stored.double(), 1).numpy()).max() <= 1e-4
+    # the cross-entropy task on the same buffers (in place), given the partials
+    o_loss = ofa.DeviceBuffer((N,), np.float32); o_mean = ofa.DeviceBuffer((4,), np.float32)
+    ofa.run_phases(K.DTYPE_BF16, dims, [ofa.phase(K.TK_CE, [d_lg, d_tg, o_loss, d_part]), ofa.phase(K.TK_CE_MEAN, [o_mean, o_loss])])
+    lgr = stored.clone().requires_grad_()
+    l = F.cross_entropy(lgr, tg.long(), reduction="none"); l.mean().backward()
+    assert relmax(o_loss.download(), l.detach()) <= 1e-5
+    assert abs(o_mean.download()[0] - float(l.mean().detach())) <= 1e-5 * float(l.mean().detach())
+    assert relmax(d_lg.download(), lgr.grad) <= 2e-2
+    # both tasks in one launch give the same bits as the two launches above (and as a repeat)
+    d_lg2 = ofa.DeviceBuffer((N, V), "bf16"); d_part2 = ofa.DeviceBuffer((N, V // 128, 2), np.float32); o_loss2 = ofa.DeviceBuffer((N,), np.float32)
+    ph2 = ofa.gemm_phase(1, K.EPI_LSE, N, V, D, d_x, D, d_W, D, d_lg2, V, nsub=5)
+    ph2.p[4] = d_part2.ptr
+    ofa.run_phases(K.DTYPE_BF16, dims, [ph2, ofa.phase(K.TK_CE, [d_lg2, d_tg, o_loss2, d_part2])])
+    np.testing.assert_array_equal(d_lg.download(), d_lg2.download())
+    np.testing.assert_array_equal(o_loss.download().view(np.uint32), o_loss2.download().view(np.uint32))
+
+
 @pytest.mark.parametrize("bf,gbf,direct", [(True, False, 0), (True, True, 0), (True, False, 1), (True, True, 1), (False, False, 0)])
 def test_adamw_three_steps(ofa, K, oracle, bf, gbf, direct):
     """direct = 0: inputs staged through shared memory by bulk copies (bf16 path); 1: the loop of direct 16-byte loads"""
