@@ -170,7 +170,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--repeats", type=int, default=0, help="timed K-step launches (0 = enough for more than a second of timed work, at least 5)")
     ap.add_argument("--phase-table", action="store_true", help="also print the per-phase busy table to stderr")
-    ap.add_argument("--cfg", action="append", default=[], metavar="FIELD=INT", help="override an integer field of ofa_config (experiments, e.g. gemm_nsub=2, attn_legacy=1); the run is then not the headline configuration")
+    ap.add_argument("--cfg", action="append", default=[], metavar="FIELD=INT", help="override an integer field of ofa_config (experiments, e.g. gemm_nsub=2, head_dx_splitk=1); the run is then not the headline configuration")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1")); local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":

@@ -61,7 +61,7 @@ typedef struct {
   int grad_bf16;            /* weight gradients are written as bf16 (the all-reduce bucket format)                */
   int ext_sync;             /* 1: gradients are cut into buckets; the graph raises a "ready" flag per bucket and holds the bucket's AdamW until the matching "done" flag is raised from outside (the all-reduce) */
   int bucket_bytes;         /* target bucket size for ext_sync (0 = 25 MiB)                                       */
-  int attn_legacy;          /* 1: attention tasks on mma.sync instead of tcgen05 (kept for comparison, default 0)          */
+  int attn_legacy;          /* must be 0 (the field once selected mma.sync attention tasks kept for comparison; they are gone, the tensor-core tasks are checked against the oracle directly) */
   int adam_interleave;      /* experimental, default 0: 1 = each layer's AdamW phase inside the backward pass; n >= 2 = AdamW trickles through the backward pass, up to n tasks after every backward phase */
   int head_dx_splitk;       /* 1: compute lm_head dX as K-split partial products + reduce (experimental, default 0)     */
   int gemm_nsub;            /* consecutive 128-wide N tiles per GEMM task (0 = default)                           */

@@ -11,7 +11,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(CSRC, "libofa_b200.so")
 CLI = os.path.join(CSRC, "ofa_cli")              # the command-line host (csrc/ofa_cli.cpp), linked against LIB
 SOURCES = ["runtime.cu", "noalloc.cu"]
-HEADERS = ["common.cuh", "task_api.h", "elementwise.cuh", "gemm_tc.cuh", "attn_mma.cuh", "attn_tc.cuh", "simt_f32.cuh", "decode.cuh",
+HEADERS = ["common.cuh", "task_api.h", "elementwise.cuh", "gemm_tc.cuh", "attn_common.cuh", "attn_tc.cuh", "simt_f32.cuh", "decode.cuh",
            "megakernel.cuh", os.path.join("..", "..", "include", "ofa_b200.h")]
 
 

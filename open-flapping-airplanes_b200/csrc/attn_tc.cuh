@@ -1,7 +1,7 @@
 // Causal flash-attention for bf16 activations, head dim 64, on the 5th-generation tensor cores: forward, dK/dV and dQ tasks
 // built from tcgen05.mma with accumulators in tensor memory, operands staged by TMA, and one softmax thread per row.
 //
-// Numerics are those of the mma.sync tasks in attn_mma.cuh (which follow llm/attention/attention.cuh:81-516): S = Q K^T in
+// Numerics follow the reference's tiles (llm/attention/attention.cuh:81-516): S = Q K^T in
 // fp32, scaled by 0.125*log2(e), exponentiated in the exp2 domain with a running row maximum; P rounded to bf16 before P.V;
 // O normalised in fp32 and rounded once; lse in natural log; backward recomputes P from lse, forms dS = P * (dP - D) in fp32,
 // rounds P and dS to bf16 before the dV / dK / dQ products, and applies the 1/8 scale to dQ and dK at the end.
@@ -26,7 +26,7 @@
 // All waits are bounded (mbar_wait); a role that gives up leaves its loop and meets the others at the closing barrier.
 #pragma once
 #include <cuda.h>
-#include "attn_mma.cuh"
+#include "attn_common.cuh"
 #include "gemm_tc.cuh"
 
 namespace ofa {

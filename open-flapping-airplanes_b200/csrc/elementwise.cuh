@@ -62,125 +62,153 @@ __device__ __forceinline__ void embed_fwd_task(int task, T* x, const T* wte, con
 }
 
 // ---------------------------------------------------------------------------------------------- LayerNorm
-// A warp owns a row; lane l holds vectors l, l+32, ... of the row (NV of them, the tail predicated off for narrow rows).
+// Task = 16 rows, two per warp. A task is a handful of microseconds long and latency-bound (16 resident warps per SM, every
+// load a round trip to L2 or HBM), so both rows of a warp are FETCHED before anything is computed: a lane keeps its share of a
+// row as raw 16-byte vectors (vectors lane, lane+32, ... of the row) and converts them when it needs them, which keeps two
+// rows (and for the backward task two operands per row) in flight at a time without running out of registers.
+// Semantics are the reference's (llm/elementwise/ew_layernorm.cuh:38-173): gamma only, eps 1e-5, fp32 statistics, two-pass
+// variance; backward dx = rstd * (g - mean(g) - xhat * mean(g * xhat)) [+ dres] with g = dy * gamma.
 template <class T, int D> struct RowRegs {
   static constexpr int VN = Vec<T>::N;
   static constexpr int VPR = D / VN;                 // vectors per row
   static constexpr int NV = (VPR + 31) / 32;         // vectors per lane
 };
-
-// y = (x - mean) * rstd * gamma, saves mean/rstd. Task = 16 rows (warp w: rows w and w+8).
-template <class T, int D>
-__device__ __forceinline__ void ln_fwd_task(int task, T* y, float* mean_o, float* rstd_o, const T* x, const T* gamma, int N) {
+template <class T, int D> struct RowShare {          // one lane's share of one row, raw
   using R = RowRegs<T, D>;
+  uint4 raw[R::NV];
+  __device__ __forceinline__ void fetch(const T* row, int lane) {
+#pragma unroll
+    for (int v = 0; v < R::NV; v++) {
+      const int vi = v * 32 + lane;
+      raw[v] = vi < R::VPR ? *reinterpret_cast<const uint4*>(row + vi * R::VN) : make_uint4(0, 0, 0, 0);
+    }
+  }
+  __device__ __forceinline__ void get(int v, float* f) const {
+    if constexpr (sizeof(T) == 2) unpack8(raw[v], f);
+    else { f[0] = __uint_as_float(raw[v].x); f[1] = __uint_as_float(raw[v].y); f[2] = __uint_as_float(raw[v].z); f[3] = __uint_as_float(raw[v].w); }
+  }
+  static __device__ __forceinline__ bool has(int v, int lane) { return v * 32 + lane < R::VPR; }
+};
+// two independent butterfly sums at once (the shuffles of one hide behind the other's)
+__device__ __forceinline__ void warp_sum2(float& a, float& b) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) { a += __shfl_xor_sync(0xffffffffu, a, o); b += __shfl_xor_sync(0xffffffffu, b, o); }
+}
+
+// y = (x - mean) * rstd * gamma, saves mean / rstd. Warp w: rows w and w + 8 of the task.
+template <class T, int D>
+__device__ __noinline__ void ln_fwd_task(int task, T* y, float* mean_o, float* rstd_o, const T* x, const T* gamma, int N) {
+  using R = RowRegs<T, D>;
+  using S = RowShare<T, D>;
   constexpr int VN = R::VN, NV = R::NV;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-#pragma unroll 1
-  for (int j = 0; j < 2; j++) {
-    const int r = task * ROWS_PER_TASK + warp + j * 8;
-    if (r >= N) continue;
-    float f[NV][VN];
-    float s = 0.f;
+  const int row[2] = {task * ROWS_PER_TASK + warp, task * ROWS_PER_TASK + warp + 8};
+  S in[2], gm;
 #pragma unroll
-    for (int v = 0; v < NV; v++) {
-      const int vi = v * 32 + lane;
-      if (vi < R::VPR) {
-        ldv(x + (size_t)r * D + vi * VN, f[v]);
+  for (int j = 0; j < 2; j++) if (row[j] < N) in[j].fetch(x + (size_t)row[j] * D, lane);
+  gm.fetch(gamma, lane);
+  float sum[2] = {0.f, 0.f};
 #pragma unroll
-        for (int k = 0; k < VN; k++) s += f[v][k];
-      }
+  for (int j = 0; j < 2; j++)
+    if (row[j] < N) {
+#pragma unroll
+      for (int v = 0; v < NV; v++) { float f[VN]; in[j].get(v, f);
+#pragma unroll
+        for (int k = 0; k < VN; k++) sum[j] += f[k]; }     // absent vectors are zero
     }
-    const float mean = warp_sum(s) * (1.f / D);
-    float q = 0.f;
+  warp_sum2(sum[0], sum[1]);
+  const float mean[2] = {sum[0] * (1.f / D), sum[1] * (1.f / D)};
+  float sq[2] = {0.f, 0.f};
+#pragma unroll
+  for (int j = 0; j < 2; j++)
+    if (row[j] < N) {
+#pragma unroll
+      for (int v = 0; v < NV; v++)
+        if (S::has(v, lane)) { float f[VN]; in[j].get(v, f);
+#pragma unroll
+          for (int k = 0; k < VN; k++) { const float d = f[k] - mean[j]; sq[j] += d * d; } }
+    }
+  warp_sum2(sq[0], sq[1]);
+#pragma unroll
+  for (int j = 0; j < 2; j++) {
+    if (row[j] >= N) continue;
+    const float rstd = rsqrtf(sq[j] * (1.f / D) + 1e-5f);
 #pragma unroll
     for (int v = 0; v < NV; v++)
-      if (v * 32 + lane < R::VPR) {
+      if (S::has(v, lane)) {
+        float f[VN], g[VN];
+        in[j].get(v, f); gm.get(v, g);
 #pragma unroll
-        for (int k = 0; k < VN; k++) { const float d = f[v][k] - mean; q += d * d; }
+        for (int k = 0; k < VN; k++) f[k] = (f[k] - mean[j]) * rstd * g[k];
+        stv(y + (size_t)row[j] * D + (v * 32 + lane) * VN, f);
       }
-    const float rstd = rsqrtf(warp_sum(q) * (1.f / D) + 1e-5f);
-#pragma unroll
-    for (int v = 0; v < NV; v++) {
-      const int vi = v * 32 + lane;
-      if (vi < R::VPR) {
-        float g[VN], o[VN];
-        ldv(gamma + vi * VN, g);
-#pragma unroll
-        for (int k = 0; k < VN; k++) o[k] = (f[v][k] - mean) * rstd * g[k];
-        stv(y + (size_t)r * D + vi * VN, o);
-      }
-    }
-    if (lane == 0) { mean_o[r] = mean; rstd_o[r] = rstd; }
+    if (lane == 0) { mean_o[row[j]] = mean[j]; rstd_o[row[j]] = rstd; }
   }
 }
 
 template <int D> __host__ __device__ constexpr size_t ln_bwd_smem_bytes() { return 8 * (size_t)D * sizeof(float); }
 
-// dx = rstd * (g - mean(g) - xhat * mean(g * xhat)) [+ dres],  g = dy * gamma,  xhat = (x - mean) * rstd.
-// Also writes this task's dgamma partial [task, D] = sum over its rows of dy * xhat (8 warps summed in index order).
+// dx, and this task's dgamma partial [task, D] = sum over its rows of dy * xhat (the eight warps' shares added in warp order).
+// A row's three operands (x, dy, dres) are fetched together before anything is computed; pass 1 forms the two row sums and
+// the dgamma terms, pass 2 recomputes xhat and g from the raw vectors (a few FMAs) instead of keeping them. The two rows of a
+// warp go one after the other: with both in flight the persistent kernel's 128-register budget spilled.
 template <class T, int D>
-__device__ __forceinline__ void ln_bwd_task(int task, T* dx, float* dgamma_part, const T* dy, const T* x, const float* mean,
+__device__ __noinline__ void ln_bwd_task(int task, T* dx, float* dgamma_part, const T* dy, const T* x, const float* mean,
                                             const float* rstd, const T* gamma, const T* dres, int N, unsigned char* smem) {
   using R = RowRegs<T, D>;
+  using S = RowShare<T, D>;
   constexpr int VN = R::VN, NV = R::NV;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   float* sdg = reinterpret_cast<float*>(smem);   // [8][D]
-  float gam[NV][VN], dg[NV][VN];
+  S gm;
+  gm.fetch(gamma, lane);
+  float dg[NV][VN];
 #pragma unroll
-  for (int v = 0; v < NV; v++) {
-    const int vi = v * 32 + lane;
-    if (vi < R::VPR) ldv(gamma + vi * VN, gam[v]);
+  for (int v = 0; v < NV; v++)
 #pragma unroll
     for (int k = 0; k < VN; k++) dg[v][k] = 0.f;
-  }
 #pragma unroll 1
   for (int j = 0; j < 2; j++) {
     const int r = task * ROWS_PER_TASK + warp + j * 8;
     if (r >= N) continue;
+    S xin, gin, res;
+    xin.fetch(x + (size_t)r * D, lane); gin.fetch(dy + (size_t)r * D, lane);
+    if (dres) res.fetch(dres + (size_t)r * D, lane);
     const float mu = mean[r], rs = rstd[r];
-    float xh[NV][VN], g[NV][VN];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-    for (int v = 0; v < NV; v++) {
-      const int vi = v * 32 + lane;
-      if (vi < R::VPR) {
-        float dyv[VN];
-        ldv(x + (size_t)r * D + vi * VN, xh[v]);
-        ldv(dy + (size_t)r * D + vi * VN, dyv);
+    for (int v = 0; v < NV; v++)
+      if (S::has(v, lane)) {
+        float xv[VN], dv[VN], gv[VN];
+        xin.get(v, xv); gin.get(v, dv); gm.get(v, gv);
 #pragma unroll
         for (int k = 0; k < VN; k++) {
-          xh[v][k] = (xh[v][k] - mu) * rs;
-          g[v][k] = dyv[k] * gam[v][k];
-          s1 += g[v][k]; s2 += g[v][k] * xh[v][k];
-          dg[v][k] += dyv[k] * xh[v][k];
+          const float xh = (xv[k] - mu) * rs, g = dv[k] * gv[k];
+          s1 += g; s2 += g * xh;
+          dg[v][k] += dv[k] * xh;
         }
       }
-    }
-    s1 = warp_sum(s1) * (1.f / D); s2 = warp_sum(s2) * (1.f / D);
+    warp_sum2(s1, s2);
+    const float m1 = s1 * (1.f / D), m2 = s2 * (1.f / D);
 #pragma unroll
-    for (int v = 0; v < NV; v++) {
-      const int vi = v * 32 + lane;
-      if (vi < R::VPR) {
-        float o[VN];
+    for (int v = 0; v < NV; v++)
+      if (S::has(v, lane)) {
+        float xv[VN], dv[VN], gv[VN], o[VN];
+        xin.get(v, xv); gin.get(v, dv); gm.get(v, gv);
 #pragma unroll
-        for (int k = 0; k < VN; k++) o[k] = rs * (g[v][k] - s1 - xh[v][k] * s2);
-        if (dres) {
-          float e[VN]; ldv(dres + (size_t)r * D + vi * VN, e);
+        for (int k = 0; k < VN; k++) { const float xh = (xv[k] - mu) * rs; o[k] = rs * (dv[k] * gv[k] - m1 - xh * m2); }
+        if (dres) { float e[VN]; res.get(v, e);
 #pragma unroll
-          for (int k = 0; k < VN; k++) o[k] += e[k];
-        }
-        stv(dx + (size_t)r * D + vi * VN, o);
+          for (int k = 0; k < VN; k++) o[k] += e[k]; }
+        stv(dx + (size_t)r * D + (v * 32 + lane) * VN, o);
       }
-    }
   }
 #pragma unroll
-  for (int v = 0; v < NV; v++) {
-    const int vi = v * 32 + lane;
-    if (vi < R::VPR) {
+  for (int v = 0; v < NV; v++)
+    if (S::has(v, lane)) {
 #pragma unroll
-      for (int k = 0; k < VN; k++) sdg[warp * D + vi * VN + k] = dg[v][k];
+      for (int k = 0; k < VN; k++) sdg[warp * D + (v * 32 + lane) * VN + k] = dg[v][k];
     }
-  }
   __syncthreads();
   for (int c = threadIdx.x; c < D; c += NTHR) {
     float s = 0.f;
@@ -191,14 +219,21 @@ __device__ __forceinline__ void ln_bwd_task(int task, T* dx, float* dgamma_part,
   __syncthreads();
 }
 
-// dgamma[c] (=|+=) sum_b part[b, c] in index order. Task = 256 columns. GT = gradient storage type (float, or bf16 bucket).
+// dgamma[c] (=|+=) sum_b part[b, c], the partials taken in a fixed order: four interleaved running sums (b mod 4), so that four
+// loads are in flight per thread instead of one, added at the end. Task = 256 columns. GT = gradient storage type.
 template <class GT>
 __device__ __forceinline__ void ln_dgamma_reduce_task(int task, GT* dgamma, const float* part, int nblk, int D, int accumulate) {
   const int c = task * NTHR + threadIdx.x;
   if (c < D) {
-    float s = 0.f;
-    for (int b = 0; b < nblk; b++) s += part[(size_t)b * D + c];
-    dgamma[c] = from_f<GT>(accumulate ? to_f(dgamma[c]) + s : s);
+    float s[4] = {0.f, 0.f, 0.f, 0.f};
+    int b = 0;
+    for (; b + 4 <= nblk; b += 4) {
+#pragma unroll
+      for (int q = 0; q < 4; q++) s[q] += part[(size_t)(b + q) * D + c];
+    }
+    for (; b < nblk; b++) s[b & 3] += part[(size_t)b * D + c];
+    const float tot = (s[0] + s[1]) + (s[2] + s[3]);
+    dgamma[c] = from_f<GT>(accumulate ? to_f(dgamma[c]) + tot : tot);
   }
 }
 
@@ -436,48 +471,70 @@ __device__ __forceinline__ float ce_mean_task(float* mean_loss, const float* los
 // ---------------------------------------------------------------------------------------------- embedding backward
 __host__ __device__ constexpr size_t embed_bwd_wte_smem_bytes(int N) { return 1024 + 5 * (size_t)N; }
 
-// dwte32[v,:] (=|+=) sum over tokens n with tok[n] == v of dx0[n,:], added in increasing n. Task = 128 vocabulary rows:
-// the block scans all N tokens, compacts the matches in token order, then each warp owns rows w, w+8, ... and accumulates
-// their tokens in registers. Without `accumulate` every row of the chunk is written (zeros where the token is absent), so
-// the gradient buffer needs no clearing between steps.
+// dwte[v,:] (=|+=) sum over tokens n with tok[n] == v of dx0[n,:], added in increasing n (the reference's order,
+// llm/elementwise/ew_loss.cuh:101-177, so that the sum does not depend on the schedule). Task = 128 vocabulary rows.
+//   1. Each warp looks at its own contiguous eighth of the token positions, 32 at a time: ballots count its matches (and a shared
+//      counter per row says how many each row has; most rows of a chunk have none), the eight warp counts give it its place in an
+//      ORDERED list of (position, row) pairs, and a second look at the same positions fills the list.
+//   2. A warp owns rows w, w + 8, ...; for a row with pairs it walks the list 32 entries at a time (ballot of "this entry is
+//      mine"), adding the dx0 rows in list order into registers (a lane holds vectors lane, lane + 32, ... of the row).
+// Without `accumulate` every row of the chunk is written (zeros where the token is absent), so the gradient buffer needs no
+// clearing between steps. Shared memory: 8 warp counts + 128 row counts, then int list[N], then one byte per list entry.
 template <class T, int D, class GT>
-__device__ __noinline__ void embed_bwd_wte_task(int task, GT* dwte32, const T* dx0, const int* tok, int N, int V, int accumulate,
+__device__ __noinline__ void embed_bwd_wte_task(int task, GT* dwte, const T* dx0, const int* tok, int N, int V, int accumulate,
                                                 unsigned char* smem) {
   using R = RowRegs<T, D>;
-  constexpr int VN = R::VN, NV = R::NV;                // lane owns 16-byte vectors lane, lane+32, ... of a row
-  int* cnt = reinterpret_cast<int*>(smem);           // [256]
-  int* list = reinterpret_cast<int*>(smem + 1024);   // [N] token positions, in order
-  unsigned char* rowof = smem + 1024 + 4 * (size_t)N;  // [N] row within the chunk
-  const int t = threadIdx.x, lo = task * EMB_VCHUNK;
-  const int per = (N + NTHR - 1) / NTHR, a = t * per, b = min(N, a + per);
-  int c = 0;
-  for (int n = a; n < b; n++) { const int v = tok[n] - lo; c += (unsigned)v < (unsigned)EMB_VCHUNK; }
-  cnt[t] = c;
+  constexpr int VN = R::VN, NV = R::NV;
+  int* wcnt = reinterpret_cast<int*>(smem);            // [8]
+  int* rowcnt = wcnt + 8;                              // [EMB_VCHUNK]
+  int* list = reinterpret_cast<int*>(smem + 1024);     // [N] matching positions, increasing
+  unsigned char* rowof = smem + 1024 + 4 * (size_t)N;  // [N] row within the chunk of each list entry
+  const int t = threadIdx.x, warp = t >> 5, lane = t & 31, lo = task * EMB_VCHUNK;
+  if (t < EMB_VCHUNK) rowcnt[t] = 0;
   __syncthreads();
-  int off = 0, total = 0;
-  for (int i = 0; i < NTHR; i++) { const int x = cnt[i]; if (i < t) off += x; total += x; }
-  for (int n = a; n < b; n++) {
-    const int v = tok[n] - lo;
-    if ((unsigned)v < (unsigned)EMB_VCHUNK) { list[off] = n; rowof[off] = (unsigned char)v; off++; }
+  // warp w owns positions [w * per, (w + 1) * per): its matches follow those of the warps before it, in position order
+  const int per = ((N + NTHR - 1) / NTHR) * 32, p0 = warp * per, p1 = min(N, p0 + per);
+  int mine_cnt = 0;
+#pragma unroll 4
+  for (int n = p0 + lane; n < p0 + per; n += 32) {
+    const int v = n < p1 ? tok[n] - lo : -1;
+    const bool hit = (unsigned)v < (unsigned)EMB_VCHUNK;
+    mine_cnt += __popc(__ballot_sync(0xffffffffu, hit));
+    if (hit) atomicAdd(&rowcnt[v], 1);
+  }
+  if (lane == 0) wcnt[warp] = mine_cnt;
+  __syncthreads();
+  int slot = 0, total = 0;
+#pragma unroll
+  for (int w = 0; w < NTHR / 32; w++) { const int c = wcnt[w]; total += c; if (w < warp) slot += c; }
+  for (int n = p0 + lane; n < p0 + per && mine_cnt > 0; n += 32) {      // second look at the same positions (now in L1): place the matches
+    const int v = n < p1 ? tok[n] - lo : -1;
+    const bool hit = (unsigned)v < (unsigned)EMB_VCHUNK;
+    const unsigned b = __ballot_sync(0xffffffffu, hit);
+    if (hit) { const int at = slot + __popc(b & ((1u << lane) - 1u)); list[at] = n; rowof[at] = (unsigned char)v; }
+    slot += __popc(b);
   }
   __syncthreads();
-  const int warp = t >> 5, lane = t & 31;
   for (int r = warp; r < EMB_VCHUNK; r += NTHR / 32) {
     if (lo + r >= V) break;
+    GT* dst = dwte + (size_t)(lo + r) * D;
+    const int mine = rowcnt[r];
+    if (mine == 0 && accumulate) continue;
     float acc[NV][VN];
-    GT* dst = dwte32 + (size_t)(lo + r) * D;
 #pragma unroll
     for (int v = 0; v < NV; v++) {
       const int vi = v * 32 + lane;
 #pragma unroll
       for (int k = 0; k < VN; k++) acc[v][k] = (accumulate && vi < R::VPR) ? to_f(dst[vi * VN + k]) : 0.f;
     }
-    for (int k0 = 0; k0 < total; k0 += 32) {
+    int seen = 0;
+    for (int k0 = 0; k0 < total && seen < mine; k0 += 32) {
       const int k = k0 + lane;
       unsigned m = __ballot_sync(0xffffffffu, k < total && rowof[k] == r);
+      seen += __popc(m);
       while (m) {
-        const int n = list[k0 + __ffs(m) - 1]; m &= m - 1;
-        const T* src = dx0 + (size_t)n * D;
+        const T* src = dx0 + (size_t)list[k0 + __ffs(m) - 1] * D;
+        m &= m - 1;
 #pragma unroll
         for (int v = 0; v < NV; v++) {
           const int vi = v * 32 + lane;
@@ -530,63 +587,73 @@ __device__ __forceinline__ AdamHP adam_hp(const AdamConst& h, int step) {
   hp.grad_scale = h.grad_scale; hp.step = step + 1; return hp;
 }
 
-// torch.optim.AdamW (non-fused, non-amsgrad) operation order on fp32 master weights:
+// torch.optim.AdamW (non-fused, non-amsgrad) operation order on fp32 master weights, as the reference keeps it
+// (llm/elementwise/ew_adamw.cuh:20-67):
 //   p *= 1 - lr*wd (unless the element lies in a no-decay range) ; m += (g - m)(1 - b1) ; v = fma(v, b2, (1 - b2) g^2) ;
 //   p -= lr/(1 - b1^t) * m / (sqrt(v)/sqrt(1 - b2^t) + eps)          (bias corrections in double)
-// then refreshes the working copy Wact (type T) that forward, backward and the decoder read. The gradient is read as GT
-// (fp32 single-GPU buffer, or the all-reduced bf16 bucket) and multiplied by hp.grad_scale (1/world size).
+// then the working copy Wact (type T) that forward, backward and the decoder read is refreshed. The gradient is read as GT
+// (fp32 single-GPU buffer, or the all-reduced bf16 bucket) and multiplied by grad_scale (1/world size).
 // nodecay: sorted disjoint [start,end) element ranges relative to W. Task = 65,536 elements; n and ranges multiples of 4.
+struct AdamMath {                     // the per-task constants and the four-element update shared by both task bodies
+  float step_size, inv_sqrt_bc2, decay_mul, one_minus_b1, one_minus_b2, b2, eps, gscale;
+  const int2* nd; int n_nd, first_nd; bool any_nd;
+  __device__ __forceinline__ void init(const AdamHP& hp, const int2* nodecay, int n_nodecay, size_t chunk_begin, size_t chunk_end) {
+    const double bc1 = 1.0 - pow((double)hp.beta1, (double)hp.step), bc2 = 1.0 - pow((double)hp.beta2, (double)hp.step);
+    step_size = (float)((double)hp.lr / bc1);
+    inv_sqrt_bc2 = (float)(1.0 / sqrt(bc2));
+    decay_mul = 1.f - hp.lr * hp.weight_decay;
+    one_minus_b1 = 1.f - hp.beta1; one_minus_b2 = 1.f - hp.beta2; b2 = hp.beta2; eps = hp.eps; gscale = hp.grad_scale;
+    nd = nodecay; n_nd = n_nodecay;
+    int lo = 0, hi = n_nodecay;       // first range whose end lies beyond the chunk start
+    while (lo < hi) { const int mid = (lo + hi) >> 1; if ((size_t)nodecay[mid].y <= chunk_begin) lo = mid + 1; else hi = mid; }
+    first_nd = lo;
+    any_nd = lo < n_nodecay && (size_t)nodecay[lo].x < chunk_end;
+  }
+  __device__ __forceinline__ bool decays(size_t idx) const {
+    if (!any_nd) return true;
+    int ri = first_nd;
+    while (ri < n_nd && (size_t)nd[ri].y <= idx) ri++;
+    return !(ri < n_nd && idx >= (size_t)nd[ri].x);
+  }
+  __device__ __forceinline__ void update4(size_t i, float* w, const float* g, float* m, float* v) const {
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+      const float gg = g[k] * gscale;
+      const float p = decays(i + k) ? w[k] * decay_mul : w[k];
+      m[k] = m[k] + (gg - m[k]) * one_minus_b1;
+      v[k] = fmaf(v[k], b2, one_minus_b2 * gg * gg);
+      w[k] = p - step_size * (m[k] / (sqrtf(v[k]) * inv_sqrt_bc2 + eps));
+    }
+  }
+};
+// elements [begin, end) with loads issued by the threads themselves (the fp32 preset, and the ragged end of a staged task)
+template <class T, class GT>
+__device__ __forceinline__ void adamw_span_direct(const AdamMath& A, size_t begin, size_t end, float* W, const GT* G, float* M, float* Vv, T* Wact) {
+#pragma unroll 4
+  for (size_t i = begin + (size_t)threadIdx.x * 4; i < end; i += NTHR * 4) {
+    float w[4], g[4], m[4], v[4];
+    ld4(W + i, w); ld4(G + i, g); ld4(M + i, m); ld4(Vv + i, v);
+    A.update4(i, w, g, m, v);
+    st4(W + i, w); st4(M + i, m); st4(Vv + i, v); st4(Wact + i, w);
+  }
+}
 template <class T, class GT>
 __device__ __forceinline__ void adamw_task(int task, float* W, const GT* G, float* M, float* Vv, T* Wact, size_t n, AdamHP hp,
                                            const int2* nodecay, int n_nodecay) {
   const size_t cs = (size_t)task * OPT_CHUNK;
   if (cs >= n) return;
   const size_t ce = cs + OPT_CHUNK < n ? cs + OPT_CHUNK : n;
-  const double bc1 = 1.0 - pow((double)hp.beta1, (double)hp.step);
-  const double bc2 = 1.0 - pow((double)hp.beta2, (double)hp.step);
-  const float step_size = (float)((double)hp.lr / bc1);
-  const float inv_sqrt_bc2 = (float)(1.0 / sqrt(bc2));
-  const float decay_mul = 1.f - hp.lr * hp.weight_decay;
-  const float omb1 = 1.f - hp.beta1, omb2 = 1.f - hp.beta2;
-  const float gs = hp.grad_scale;
-  int lo = 0;
-  {  // first range whose end lies beyond the chunk start
-    int hi = n_nodecay;
-    while (lo < hi) { const int mid = (lo + hi) >> 1; if ((size_t)nodecay[mid].y <= cs) lo = mid + 1; else hi = mid; }
-  }
-  const bool any_nd = lo < n_nodecay && (size_t)nodecay[lo].x < ce;
-#pragma unroll 4
-  for (size_t i = cs + (size_t)threadIdx.x * 4; i < ce; i += NTHR * 4) {
-    float w[4], g[4], m[4], v[4];
-    ld4(W + i, w); ld4(G + i, g); ld4(M + i, m); ld4(Vv + i, v);
-#pragma unroll
-    for (int k = 0; k < 4; k++) {
-      bool dec = true;
-      if (any_nd) {
-        const int idx = (int)(i + k);
-        int ri = lo;
-        while (ri < n_nodecay && nodecay[ri].y <= idx) ri++;
-        if (ri < n_nodecay && idx >= nodecay[ri].x) dec = false;
-      }
-      const float gg = g[k] * gs;
-      const float p = dec ? w[k] * decay_mul : w[k];
-      m[k] = m[k] + (gg - m[k]) * omb1;
-      v[k] = fmaf(v[k], hp.beta2, omb2 * gg * gg);
-      const float denom = sqrtf(v[k]) * inv_sqrt_bc2 + hp.eps;
-      w[k] = p - step_size * (m[k] / denom);
-    }
-    st4(W + i, w); st4(M + i, m); st4(Vv + i, v); st4(Wact + i, w);
-  }
+  AdamMath A; A.init(hp, nodecay, n_nodecay, cs, ce);
+  adamw_span_direct<T, GT>(A, cs, ce, W, G, M, Vv, Wact);
 }
 
 // The same update with the inputs staged through shared memory by the copy engine. A block has 8 warps and each thread can keep
 // only a few 16-byte loads in flight, so the loop above runs at what 256 threads can request, not at what HBM can deliver
-// (measured: 0.71 of the copy bandwidth with every block of the GPU running it). Here one thread queues bulk copies
+// (measured: 0.71 of the copy bandwidth with every block of the GPU running it, 0.90 staged). One thread queues bulk copies
 // (cp.async.bulk, completion counted on an mbarrier) of W, M, V and G for tiles of 2,048 elements, three tiles (96 KB) ahead
-// of the arithmetic; the threads read their operands from shared memory and write results straight to global memory. The
-// arithmetic and its order are those of adamw_task, element for element. `bar0` = three block-private mbarriers (count 1),
-// `tiles` = running count of tiles this block has staged since it started (advanced identically by every thread).
-// The ragged end of a range (fewer than 2,048 elements, or byte counts that are not multiples of 16) goes through the loop above.
+// of the arithmetic; the threads read their operands from shared memory and write results straight to global memory.
+// `bar0` = three block-private mbarriers (count 1), `tiles` = running count of tiles this block has staged since it started
+// (advanced identically by every thread). The ragged end of a range (fewer than 2,048 elements) goes through the direct loop.
 constexpr int ADAM_TILE = 2048, ADAM_STAGES = 3, ADAM_STAGE_BYTES = 32768;
 template <class T, class GT>
 __device__ __forceinline__ void adamw_task_bulk(int task, float* W, const GT* G, float* M, float* Vv, T* Wact, size_t n, AdamHP hp,
@@ -595,37 +662,7 @@ __device__ __forceinline__ void adamw_task_bulk(int task, float* W, const GT* G,
   const size_t cs = (size_t)task * OPT_CHUNK;
   if (cs >= n) return;
   const size_t ce = cs + OPT_CHUNK < n ? cs + OPT_CHUNK : n;
-  const double bc1 = 1.0 - pow((double)hp.beta1, (double)hp.step);
-  const double bc2 = 1.0 - pow((double)hp.beta2, (double)hp.step);
-  const float step_size = (float)((double)hp.lr / bc1);
-  const float inv_sqrt_bc2 = (float)(1.0 / sqrt(bc2));
-  const float decay_mul = 1.f - hp.lr * hp.weight_decay;
-  const float omb1 = 1.f - hp.beta1, omb2 = 1.f - hp.beta2;
-  const float gs = hp.grad_scale, b2 = hp.beta2, eps = hp.eps;
-  int lo = 0;
-  {
-    int hi = n_nodecay;
-    while (lo < hi) { const int mid = (lo + hi) >> 1; if ((size_t)nodecay[mid].y <= cs) lo = mid + 1; else hi = mid; }
-  }
-  const bool any_nd = lo < n_nodecay && (size_t)nodecay[lo].x < ce;
-  auto update4 = [&](size_t i, float* w, const float* g, float* m, float* v) {
-#pragma unroll
-    for (int k = 0; k < 4; k++) {
-      bool dec = true;
-      if (any_nd) {
-        const int idx = (int)(i + k);
-        int ri = lo;
-        while (ri < n_nodecay && nodecay[ri].y <= idx) ri++;
-        if (ri < n_nodecay && idx >= nodecay[ri].x) dec = false;
-      }
-      const float gg = g[k] * gs;
-      const float p = dec ? w[k] * decay_mul : w[k];
-      m[k] = m[k] + (gg - m[k]) * omb1;
-      v[k] = fmaf(v[k], b2, omb2 * gg * gg);
-      const float denom = sqrtf(v[k]) * inv_sqrt_bc2 + eps;
-      w[k] = p - step_size * (m[k] / denom);
-    }
-  };
+  AdamMath A; A.init(hp, nodecay, n_nodecay, cs, ce);
   const int tid = threadIdx.x;
   const bool aligned = ((reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(M) | reinterpret_cast<uintptr_t>(Vv) | reinterpret_cast<uintptr_t>(G)) & 15) == 0;
   const int nfull = aligned ? (int)((ce - cs) / ADAM_TILE) : 0;
@@ -655,7 +692,7 @@ __device__ __forceinline__ void adamw_task_bulk(int task, float* W, const GT* G,
         float w[4], g[4], m[4], v[4];
         ld4(reinterpret_cast<const float*>(sp) + e, w); ld4(reinterpret_cast<const float*>(sp + 8192) + e, m);
         ld4(reinterpret_cast<const float*>(sp + 16384) + e, v); ld4(reinterpret_cast<const GT*>(sp + 24576) + e, g);
-        update4(i0 + e, w, g, m, v);
+        A.update4(i0 + e, w, g, m, v);
         st4(W + i0 + e, w); st4(M + i0 + e, m); st4(Vv + i0 + e, v); st4(Wact + i0 + e, w);
       }
     }
@@ -670,13 +707,7 @@ __device__ __forceinline__ void adamw_task_bulk(int task, float* W, const GT* G,
     }
     if (tid == 0 && k + ADAM_STAGES < nfull) { fence_proxy_async(); issue(k + ADAM_STAGES); }
   }
-  // the ragged end
-  for (size_t i = cs + (size_t)nfull * ADAM_TILE + (size_t)tid * 4; i < ce; i += NTHR * 4) {
-    float w[4], g[4], m[4], v[4];
-    ld4(W + i, w); ld4(G + i, g); ld4(M + i, m); ld4(Vv + i, v);
-    update4(i, w, g, m, v);
-    st4(W + i, w); st4(M + i, m); st4(Vv + i, v); st4(Wact + i, w);
-  }
+  adamw_span_direct<T, GT>(A, cs + (size_t)nfull * ADAM_TILE, ce, W, G, M, Vv, Wact);
 }
 
 // out[i] = T(part0[i] + part1[i] + ...) in index order: the reduce of a split-K GEMM. Task = 16,384 elements (n % 8 == 0).

@@ -18,7 +18,7 @@
 #include "task_api.h"
 #include "elementwise.cuh"
 #include "gemm_tc.cuh"
-#include "attn_mma.cuh"
+#include "attn_common.cuh"
 #include "attn_tc.cuh"
 #include "simt_f32.cuh"
 #include "decode.cuh"
@@ -51,8 +51,7 @@ __device__ __forceinline__ void run_train_task(const Ctx& C, const PhaseDesc& d,
       if constexpr (IsBf16<T>::value) {
         const int BH = md.B * md.H, QT = md.T / attn::QTILE;
         const int qt = QT - 1 - local / BH, bh = local % BH;      // heavy (late) query tiles first
-        if (d.p[6]) attn_tc::fwd_task((const attn_tc::Maps*)d.p[6], (bf16*)d.p[1], (float*)d.p[2], bh / md.H, bh % md.H, qt, md.T, md.H, smem, ap, gp.tmem_base, C.status, ph, local);
-        else attn::fwd_task((const bf16*)d.p[0], (bf16*)d.p[1], (float*)d.p[2], bh / md.H, bh % md.H, qt, md.T, md.H, smem);
+        attn_tc::fwd_task((const attn_tc::Maps*)d.p[6], (bf16*)d.p[1], (float*)d.p[2], bh / md.H, bh % md.H, qt, md.T, md.H, smem, ap, gp.tmem_base, C.status, ph, local);
       } else {
         f32::attn_fwd_task<DH>((const float*)d.p[0], (float*)d.p[1], (float*)d.p[2], local / md.H, local % md.H, md.T, md.H, smem);
       }
@@ -71,14 +70,10 @@ __device__ __forceinline__ void run_train_task(const Ctx& C, const PhaseDesc& d,
         const int BH = md.B * md.H, QT = md.T / attn::QTILE;
         if (local < BH * QT) {                                     // dK/dV: early key tiles see the most queries -> first
           const int kt = local / BH, bh = local % BH;
-          if (d.p[6]) attn_tc::bwd_dkdv_task((const attn_tc::Maps*)d.p[6], (const float*)d.p[2], (const float*)d.p[3], (bf16*)d.p[4], bh / md.H, bh % md.H, kt, md.T, md.H, smem, ap, gp.tmem_base, C.status, ph, local);
-          else attn::bwd_dkdv_task((const bf16*)d.p[0], (const bf16*)d.p[1], (const float*)d.p[2], (const float*)d.p[3], (bf16*)d.p[4],
-                              bh / md.H, bh % md.H, kt, md.T, md.H, smem);
+          attn_tc::bwd_dkdv_task((const attn_tc::Maps*)d.p[6], (const float*)d.p[2], (const float*)d.p[3], (bf16*)d.p[4], bh / md.H, bh % md.H, kt, md.T, md.H, smem, ap, gp.tmem_base, C.status, ph, local);
         } else {                                                   // dQ: late query tiles see the most keys -> first
           const int l2 = local - BH * QT, qt = QT - 1 - l2 / BH, bh = l2 % BH;
-          if (d.p[6]) attn_tc::bwd_dq_task((const attn_tc::Maps*)d.p[6], (const float*)d.p[2], (const float*)d.p[3], (bf16*)d.p[4], bh / md.H, bh % md.H, qt, md.T, md.H, smem, ap, gp.tmem_base, C.status, ph, local);
-          else attn::bwd_dq_task((const bf16*)d.p[0], (const bf16*)d.p[1], (const float*)d.p[2], (const float*)d.p[3], (bf16*)d.p[4],
-                            bh / md.H, bh % md.H, qt, md.T, md.H, smem);
+          attn_tc::bwd_dq_task((const attn_tc::Maps*)d.p[6], (const float*)d.p[2], (const float*)d.p[3], (bf16*)d.p[4], bh / md.H, bh % md.H, qt, md.T, md.H, smem, ap, gp.tmem_base, C.status, ph, local);
         }
       } else {
         f32::attn_bwd_task<DH>((const float*)d.p[0], (const float*)d.p[5], (const float*)d.p[1], (const float*)d.p[2], (float*)d.p[4],

@@ -445,7 +445,7 @@ bool build_train_graph(ofa_ctx* c) {
       addp(s + "ln1", d, {prev}, {opt_layer(l)}, {prev}); }
     addp(s + "qkv", mkgemm(GL_NN, GE_STORE, ln1[l], D, Wact + lay.wqkv[l], 3 * D, qkv[l], 3 * D, nullptr, 0, N, 3 * D, D, 0), {s + "ln1"}, {}, {s + "ln1"});
     { PhaseDesc d = mk(TK_ATT_FWD, attn_fwd_tasks); d.p[0] = qkv[l]; d.p[1] = att[l]; d.p[2] = lse[l];
-      if (bf && !cfg.attn_legacy) { std::string e; d.p[6] = const_cast<void*>(make_attn_maps(c->ar, qkv[l], nullptr, N, D, e)); if (!d.p[6]) { ok = false; err = e; } }
+      if (bf) { std::string e; d.p[6] = const_cast<void*>(make_attn_maps(c->ar, qkv[l], nullptr, N, D, e)); if (!d.p[6]) { ok = false; err = e; } }
       addp(s + "attn", d, {s + "qkv"}, {}, {s + "qkv"}); }
     addp(s + "wo+res", mkgemm(GL_NN, GE_RES, att[l], D, Wact + lay.wo[l], D, hb[l], D, xs[l], D, N, D, D, 0), {s + "attn"}, {}, {s + "attn"});
     { PhaseDesc d = mk(TK_LN_FWD, rows16); d.p[0] = ln2[l]; d.p[1] = mean2[l]; d.p[2] = rstd2[l]; d.p[3] = hb[l]; d.p[4] = Wact + lay.g2[l];
@@ -641,7 +641,7 @@ bool build_train_graph(ofa_ctx* c) {
       addb(s + "dWo", mkgemm(GL_TN, wepi, att[l], D, dh[l], D, G(lay.wo[l]), D, nullptr, 0, D, D, N, 0), {s + "ln2 bwd"}, {});
       if (!bf) { PhaseDesc d = mk(TK_ATT_PREP, 1); d.p[0] = att[l]; d.p[1] = dob[l]; d.p[2] = Dr[l]; addb(s + "attn prep", d, {s + "dO"}, {}); }
       { PhaseDesc d = mk(TK_ATT_BWD, attn_bwd_tasks); d.p[0] = qkv[l]; d.p[1] = dob[l]; d.p[2] = lse[l]; d.p[3] = Dr[l]; d.p[4] = dqkv[l]; d.p[5] = att[l];
-        if (bf && !cfg.attn_legacy) { std::string e; d.p[6] = const_cast<void*>(make_attn_maps(c->ar, qkv[l], dob[l], N, D, e)); if (!d.p[6]) { ok = false; err = e; } }
+        if (bf) { std::string e; d.p[6] = const_cast<void*>(make_attn_maps(c->ar, qkv[l], dob[l], N, D, e)); if (!d.p[6]) { ok = false; err = e; } }
         addb(s + "attn bwd", d, {bf ? s + "dO" : s + "attn prep"}, {}, {s + "dO"}); }
       addb(s + "dln1", mkgemm(GL_NT, GE_STORE, dqkv[l], 3 * D, Wact + lay.wqkv[l], 3 * D, dln1[l], D, nullptr, 0, N, D, 3 * D, 0), {s + "attn bwd"}, {}, {s + "attn bwd"});
       addb(s + "dWqkv", mkgemm(GL_TN, wepi, ln1[l], D, dqkv[l], 3 * D, G(lay.wqkv[l]), 3 * D, nullptr, 0, D, 3 * D, N, 0), {s + "attn bwd"}, {});
@@ -892,6 +892,7 @@ extern "C" int ofa_create(const ofa_config* cfg, ofa_ctx** out) {
   if (cfg->mode < 0 || cfg->mode > 3) return bail(OFA_BAD_CONFIG, "bad mode");
   if (cfg->mode == OFA_MODE_DECODE_ONLY && !cfg->use_decode) return bail(OFA_BAD_CONFIG, "decode-only mode needs use_decode");
   if (cfg->dp_world < 1) return bail(OFA_BAD_CONFIG, "dp_world < 1");
+  if (cfg->attn_legacy) return bail(OFA_BAD_CONFIG, "attn_legacy: the mma.sync attention tasks are no longer part of the library");
 
   c->device = cfg->device;
   const bool dry = cfg->device < 0;      // planning mode: build layout, buckets and phase graphs without touching a device
@@ -1324,11 +1325,11 @@ extern "C" int ofa_run_phases(int dtype, const ofa_dims* dims, const ofa_phase* 
       case TK_EMBED: case TK_LN_FWD: case TK_LN_BWD: d.ntasks = rows16; break;
       case TK_LN_DG: d.ntasks = (m.D + NTHR - 1) / NTHR; break;
       case TK_ATT_FWD: d.ntasks = bf ? BH * (m.T / attn::QTILE) : BH;
-        if (bf && !s.i0) { d.p[6] = const_cast<void*>(make_attn_maps(ar, s.p[0], nullptr, m.N, m.D, err)); if (!d.p[6]) { ar.free_all(); return fail(nullptr, OFA_CUDA_ERROR, err); } }   // i0 = 1: mma.sync tasks
+        if (bf) { d.p[6] = const_cast<void*>(make_attn_maps(ar, s.p[0], nullptr, m.N, m.D, err)); if (!d.p[6]) { ar.free_all(); return fail(nullptr, OFA_CUDA_ERROR, err); } }
         break;
       case TK_ATT_PREP: d.ntasks = bf ? BH * (m.T / attn::QTILE) : 1; break;
       case TK_ATT_BWD: d.ntasks = bf ? 2 * BH * (m.T / attn::QTILE) : BH;
-        if (bf && !s.i0) { d.p[6] = const_cast<void*>(make_attn_maps(ar, s.p[0], s.p[1], m.N, m.D, err)); if (!d.p[6]) { ar.free_all(); return fail(nullptr, OFA_CUDA_ERROR, err); } }
+        if (bf) { d.p[6] = const_cast<void*>(make_attn_maps(ar, s.p[0], s.p[1], m.N, m.D, err)); if (!d.p[6]) { ar.free_all(); return fail(nullptr, OFA_CUDA_ERROR, err); } }
         break;
       case TK_CE: d.ntasks = (m.N + ew::CE_ROWS - 1) / ew::CE_ROWS;
         if (s.p[3]) { if (!bf || m.V % 128) { ar.free_all(); return fail(nullptr, OFA_BAD_ARGUMENT, "cross-entropy with softmax partials: bf16, vocab a multiple of 128"); } d.i2 = m.V / 128; }

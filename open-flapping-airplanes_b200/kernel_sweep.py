@@ -77,7 +77,6 @@ def run_gemm(ofa, name, repeats, nsub):
 
 
 REF_METHOD = False   # --ref-method: time GEMMs the way the reference's test program does (warm operands, best of several)
-ATTN_LEGACY = 0      # --attn-legacy: time the mma.sync attention tasks instead of the tcgen05 ones
 
 
 def run_attn(ofa, which, repeats):
@@ -91,10 +90,10 @@ def run_attn(ofa, which, repeats):
         o = ofa.DeviceBuffer((N, D), "bf16"); lse = ofa.DeviceBuffer((B, H, T), np.float32); Dr = ofa.DeviceBuffer((B, H, T), np.float32); dqkv = ofa.DeviceBuffer((N, 3 * D), "bf16")
         keep += [qkv, dO, o, lse, Dr, dqkv]
         if which == "attn_fwd":
-            phases.append(ofa.phase(K.TK_ATT_FWD, [qkv, o, lse], i0=ATTN_LEGACY))
+            phases.append(ofa.phase(K.TK_ATT_FWD, [qkv, o, lse]))
         else:
             ofa.run_phases(K.DTYPE_BF16, DIMS, [ofa.phase(K.TK_ATT_FWD, [qkv, o, lse])])
-            phases += [ofa.phase(K.TK_ATT_PREP, [o, dO, Dr]), ofa.phase(K.TK_ATT_BWD, [qkv, dO, lse, Dr, dqkv, o], i0=ATTN_LEGACY)]
+            phases += [ofa.phase(K.TK_ATT_PREP, [o, dO, Dr]), ofa.phase(K.TK_ATT_BWD, [qkv, dO, lse, Dr, dqkv, o])]
     ms = ofa.run_phases(K.DTYPE_BF16, DIMS, phases, repeats=repeats) / (repeats * nsets)
     fwd_flop = 4.0 * B * H * T * T * 64 / 2
     flop = fwd_flop if which == "attn_fwd" else 2.5 * fwd_flop
@@ -236,13 +235,11 @@ def main():
     ap.add_argument("--only", default="")
     ap.add_argument("--repeats", type=int, default=5)
     ap.add_argument("--nsub", type=int, default=0)
-    ap.add_argument("--attn-legacy", action="store_true")
     ap.add_argument("--list", action="store_true")
     ap.add_argument("--ref-method", action="store_true", help="GEMM cases: the reference test program's timing method (same operands repeated, best of 6)")
     ap.add_argument("--ref-vocab", action="store_true", help="GEMM cases with a vocabulary dimension use the reference's 100352 instead of 50304")
     a = ap.parse_args()
-    global ATTN_LEGACY, REF_METHOD
-    ATTN_LEGACY = 1 if a.attn_legacy else 0
+    global REF_METHOD
     REF_METHOD = a.ref_method
     if a.ref_vocab:
         for k, (l, e, m, n, kk) in list(GEMMS.items()):

@@ -280,9 +280,8 @@ def test_gemm_row_term_epilogue(ofa, K, oracle):
     assert np.abs(d_Dr.download() - d_Dr2.download()).max() <= 1e-3 * max(1.0, np.abs(ref).max())
 
 
-@pytest.mark.parametrize("legacy", [0, 1])            # 0: tcgen05 tasks (tensor-memory accumulators), 1: mma.sync tasks
 @pytest.mark.parametrize("B,T", [(2, 256), (1, 1024), (3, 128)])
-def test_attention_bf16_forward_backward(ofa, K, oracle, B, T, legacy):
+def test_attention_bf16_forward_backward(ofa, K, oracle, B, T):
     H, dh = 12, 64
     D = H * dh
     dims = dict(DIMS_S, ctx_len=T, batch=B)
@@ -292,8 +291,8 @@ def test_attention_bf16_forward_backward(ofa, K, oracle, B, T, legacy):
     d_qkv = ofa.DeviceBuffer.from_host(qkv.numpy(), "bf16"); d_dO = ofa.DeviceBuffer.from_host(dO.numpy(), "bf16")
     d_o = ofa.DeviceBuffer((N, D), "bf16"); d_lse = ofa.DeviceBuffer((B, H, T), np.float32); d_Dr = ofa.DeviceBuffer((B, H, T), np.float32)
     d_dqkv = ofa.DeviceBuffer((N, 3 * D), "bf16")
-    phases = [ofa.phase(K.TK_ATT_FWD, [d_qkv, d_o, d_lse], i0=legacy), ofa.phase(K.TK_ATT_PREP, [d_o, d_dO, d_Dr]),
-              ofa.phase(K.TK_ATT_BWD, [d_qkv, d_dO, d_lse, d_Dr, d_dqkv, d_o], i0=legacy)]
+    phases = [ofa.phase(K.TK_ATT_FWD, [d_qkv, d_o, d_lse]), ofa.phase(K.TK_ATT_PREP, [d_o, d_dO, d_Dr]),
+              ofa.phase(K.TK_ATT_BWD, [d_qkv, d_dO, d_lse, d_Dr, d_dqkv, d_o])]
     ofa.run_phases(K.DTYPE_BF16, dims, phases)
     o_ref, lse_ref = oracle.attention_ref(qkv, B, T, H, dh)
     assert relmax(d_o.download(), o_ref) <= 2e-2
@@ -307,8 +306,7 @@ def test_attention_bf16_forward_backward(ofa, K, oracle, B, T, legacy):
     np.testing.assert_array_equal(first, d_dqkv.download())
 
 
-@pytest.mark.parametrize("legacy", [0, 1])
-def test_attention_bf16_forward_with_growing_row_maxima(ofa, K, oracle, legacy):
+def test_attention_bf16_forward_with_growing_row_maxima(ofa, K, oracle):
     """Keys whose scores grow along the sequence: a row's maximum rises by far more than 2^8 from one key tile to the next, so the
     tcgen05 forward task has to rescale the output row it keeps in tensor memory (its rare path) again and again."""
     B, T, H, dh = 2, 512, 12, 64
@@ -323,7 +321,7 @@ def test_attention_bf16_forward_with_growing_row_maxima(ofa, K, oracle, legacy):
     qkv = rnd(qkv, True)
     d_qkv = ofa.DeviceBuffer.from_host(qkv.numpy(), "bf16")
     d_o = ofa.DeviceBuffer((N, D), "bf16"); d_lse = ofa.DeviceBuffer((B, H, T), np.float32)
-    ofa.run_phases(K.DTYPE_BF16, dims, [ofa.phase(K.TK_ATT_FWD, [d_qkv, d_o, d_lse], i0=legacy)])
+    ofa.run_phases(K.DTYPE_BF16, dims, [ofa.phase(K.TK_ATT_FWD, [d_qkv, d_o, d_lse])])
     o_ref, lse_ref = oracle.attention_ref(qkv, B, T, H, dh)
     spread = float(lse_ref.max() - lse_ref.min())
     assert spread > 12.0                                                   # natural log: far beyond 8 bits between the first and the last tiles
