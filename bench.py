@@ -37,7 +37,7 @@ FLOP_PER_STEP = 6 * TOKENS_PER_STEP * P_MM + L * 3.5 * (4 * B * H * T * T * (D /
 # dram__bytes_read.sum + dram__bytes_write.sum of the megakernel per step, split workload on one GPU: a constant taken from ONE ncu
 # capture of a 2-step launch (concurrent decoder included), not measured by this program. profiles/ofa_kernel_bench_split_dram_traffic.md
 # holds the command, the raw figures, the date and the commit of the capture; it has to be re-captured when the training graph changes.
-SPLIT_DRAM_BYTES_PER_STEP = 19.3e9
+SPLIT_DRAM_BYTES_PER_STEP = 20.3e9
 
 
 def measured_peaks():
@@ -169,6 +169,7 @@ def main():
                     help="ref_*: the same two workloads at the shapes the reference program is compiled for (vocab 100352 tied, context 512, batch 8), for a like-for-like line beside its own binary")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--repeats", type=int, default=0, help="timed K-step launches (0 = enough for more than a second of timed work, at least 5)")
+    ap.add_argument("--dp-side", choices=["native", "torch"], default="torch", help="N > 1: gradient all-reduce queued by the library's C++ side (its own NCCL communicator) or through torch.distributed")
     ap.add_argument("--phase-table", action="store_true", help="also print the per-phase busy table to stderr")
     ap.add_argument("--cfg", action="append", default=[], metavar="FIELD=INT", help="override an integer field of ofa_config (experiments, e.g. gemm_nsub=2, head_dx_splitk=1); the run is then not the headline configuration")
     args = ap.parse_args()
@@ -228,7 +229,8 @@ def main():
     tokens = np.random.default_rng(1000 + rank).integers(0, V, size=ntok, dtype=np.uint32)     # uniform ids, a distinct seed per rank
     mk.set_tokens(tokens)
     if world > 1:
-        dp = ofa.dp.DataParallel(mk, dist)               # NCCL gradient all-reduce ordered by device flags
+        # NCCL gradient all-reduce ordered by device flags
+        dp = ofa.dp.NativeDataParallel(mk, rank, world) if args.dp_side == "native" else ofa.dp.DataParallel(mk, dist)
 
     def barrier():
         torch.cuda.synchronize()
@@ -304,7 +306,7 @@ def main():
                        "projected_4000_steps_s": ms / K * 4000 / 1e3, **({"overrides": args.cfg} if args.cfg else {})},
             "decode_tok_s": dec_tok_s, "final_loss": float(losses[-1]), "first_loss": float(losses[0]),
             "e2e": {"value": world * TOKENS_PER_STEP * K / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": int(window.nbytes / K + starts.nbytes / K), "d2h_bytes_per_step": 4},
-            "gpu_launches": 1,
+            "gpu_launches": 2 if split else 1,   # the persistent kernel, and with the decoder its one-block residual rebuild before it
             "roofline": {"bound": "tensor", "achieved": achieved_tf, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved_tf / peak_tf,
                          "traffic": SPLIT_DRAM_BYTES_PER_STEP if (args.workload == "split" and world == 1 and not args.cfg) else None, "peak_source": f"{how} bf16_tflops_sustained x {sms_used}/148 SMs", "flop_per_step": FLOP_PER_STEP},
             "clocks": clocks,

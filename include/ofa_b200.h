@@ -147,6 +147,21 @@ int ofa_bucket_span(const ofa_ctx* ctx, int bucket, size_t* offset, size_t* coun
 void* ofa_grad_buffer(const ofa_ctx* ctx);
 int* ofa_ext_ready_flags(const ofa_ctx* ctx);
 int* ofa_ext_done_flags(const ofa_ctx* ctx);
+/* The communication side itself, for hosts without their own (no counterpart in the reference): one NCCL communicator per
+ * context, looked up at run time (environment OFA_NCCL_LIB = path of libnccl.so.2, else the NCCL the process already holds),
+ * never linked. Rank 0 obtains a 128-byte id and hands it to the other ranks by its own means; every rank calls ofa_dp_init
+ * (cfg.ext_sync = 1, cfg.dp_world = world) before its first launch. Per launch: ofa_launch(ctx, n); ofa_dp_enqueue(ctx, n) -
+ * in this order, a queued stream wait must never precede the kernel that satisfies it - then ofa_dp_wait instead of ofa_wait.
+ * ofa_dp_wait returns OFA_OK only when the kernels of ALL ranks ran to the end: the rank whose kernel stopped early returns
+ * that failure after releasing its queued waits (ofa_dp_cancel), the others OFA_DEVICE_ABORT. comm_timeout_ms bounds the drain
+ * of the communication stream and the status exchange (a missing rank gives OFA_TIMEOUT, not a hang of the host). */
+int ofa_dp_unique_id(void* out128);
+int ofa_dp_init(ofa_ctx* ctx, const void* id128, int rank, int world);
+int ofa_dp_enqueue(ofa_ctx* ctx, int nsteps);
+int ofa_dp_cancel(ofa_ctx* ctx);
+int ofa_dp_finish(ofa_ctx* ctx, int timeout_ms);
+int ofa_dp_wait(ofa_ctx* ctx, int timeout_ms, int comm_timeout_ms, ofa_status_t* status);
+void ofa_dp_shutdown(ofa_ctx* ctx);                 /* also done by ofa_destroy */
 
 /* ---- task level -------------------------------------------------------------------------------------------------- */
 enum {  /* task kinds, = TaskKind of the device code */

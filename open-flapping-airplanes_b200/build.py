@@ -11,7 +11,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(CSRC, "libofa_b200.so")
 CLI = os.path.join(CSRC, "ofa_cli")              # the command-line host (csrc/ofa_cli.cpp), linked against LIB
 SOURCES = ["runtime.cu", "noalloc.cu"]
-HEADERS = ["common.cuh", "task_api.h", "elementwise.cuh", "gemm_tc.cuh", "attn_common.cuh", "attn_tc.cuh", "simt_f32.cuh", "decode.cuh",
+HEADERS = ["common.cuh", "task_api.h", "elementwise.cuh", "gemm_tc.cuh", "attn_common.cuh", "attn_tc.cuh", "dp_nccl.inc", "simt_f32.cuh", "decode.cuh",
            "megakernel.cuh", os.path.join("..", "..", "include", "ofa_b200.h")]
 
 
@@ -34,7 +34,7 @@ def build(force=False, verbose=False):
     if not force and not needs_build():
         return LIB
     cmd = [nvcc_path(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--shared",
-           "-Xcompiler", "-fPIC", "-o", LIB] + [os.path.join(CSRC, s) for s in SOURCES]
+           "-Xcompiler", "-fPIC", "-o", LIB, "-ldl"] + [os.path.join(CSRC, s) for s in SOURCES]
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
     r = subprocess.run(cmd, capture_output=True, text=True)

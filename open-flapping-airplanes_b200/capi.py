@@ -85,6 +85,13 @@ PROTOTYPES = {
     "ofa_grad_buffer": (C.c_void_p, [C.c_void_p]),
     "ofa_ext_ready_flags": (C.c_void_p, [C.c_void_p]),
     "ofa_ext_done_flags": (C.c_void_p, [C.c_void_p]),
+    "ofa_dp_unique_id": (C.c_int, [C.c_void_p]),
+    "ofa_dp_init": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
+    "ofa_dp_enqueue": (C.c_int, [C.c_void_p, C.c_int]),
+    "ofa_dp_cancel": (C.c_int, [C.c_void_p]),
+    "ofa_dp_finish": (C.c_int, [C.c_void_p, C.c_int]),
+    "ofa_dp_wait": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.POINTER(Status)]),
+    "ofa_dp_shutdown": (None, [C.c_void_p]),
     "ofa_dev_alloc": (C.c_int, [C.POINTER(C.c_void_p), C.c_size_t]),
     "ofa_dev_free": (C.c_int, [C.c_void_p]),
     "ofa_h2d": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t]),

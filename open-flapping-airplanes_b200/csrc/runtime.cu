@@ -292,7 +292,10 @@ int smem_for(bool bf, int Tctx, int N) {
 }  // namespace
 
 // ================================================================================================ context
+struct ofa_dp_state;
+extern "C" void ofa_dp_shutdown(ofa_ctx* c);
 struct ofa_ctx {
+  ofa_dp_state* dp = nullptr;        // communication side of data parallelism (dp_nccl.inc), created by ofa_dp_init
   ofa_config cfg{};
   ModelDims md{};
   bool bf = true;
@@ -853,6 +856,7 @@ extern "C" void ofa_destroy(ofa_ctx* c) {
     for (int i = 0; i < 25000 && !done; i++) { done = cudaEventQuery(c->ev1) != cudaErrorNotReady; if (!done) { if (i % 64 == 63) post_abort(c); struct timespec sl = {0, 200000}; nanosleep(&sl, nullptr); } }
     if (!done) { delete c; return; }
   }
+  ofa_dp_shutdown(c);
   c->train_job.free_all(); c->dec_job.free_all();
   if (c->d_step_done) cudaFree(c->d_step_done);
   if (c->d_tokens) cudaFree(c->d_tokens);
@@ -1394,3 +1398,5 @@ extern "C" int ofa_bucket_span(const ofa_ctx* c, int b, size_t* offset, size_t* 
 extern "C" void* ofa_grad_buffer(const ofa_ctx* c) { return c ? (c->cfg.grad_bf16 ? (void*)c->Gbf : (void*)c->G32) : nullptr; }
 extern "C" int* ofa_ext_ready_flags(const ofa_ctx* c) { return c ? c->d_ext_ready : nullptr; }
 extern "C" int* ofa_ext_done_flags(const ofa_ctx* c) { return c ? c->d_ext_done : nullptr; }
+
+#include "dp_nccl.inc"

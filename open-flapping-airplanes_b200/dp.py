@@ -22,6 +22,9 @@ rank's queued stream waits without the `ready` values they wait for, and every p
 drains and the collectives complete with data nobody will use; afterwards the ranks exchange their status, so that every rank
 raises, not only the one whose kernel stopped. `finish()` gives up after a timeout instead of blocking for good.
 
+`NativeDataParallel` offers the same calls on top of the library's own C++ queue (ofa_dp_*: an NCCL communicator of its own,
+looked up with dlopen), for hosts that have no torch.distributed; `DataParallel` reuses the process group the host already has.
+
 The queue itself sits behind a small interface (wait for a flag value, all-reduce a span, write a flag value, raise the ready
 flags out of band, drain with a timeout). `CudaFlagQueue` implements it with stream memory operations; `HostFlagQueue` runs
 the same operations on a host thread over a numpy flag array, so the cancel and status logic is tested among CPU ranks (gloo).
@@ -259,3 +262,70 @@ class DataParallel:
             raise err
         if any_failed:
             raise DataParallelAborted("another rank's kernel stopped early: the gradients of this launch are not valid")
+
+
+def torch_nccl_library():
+    """Path of the NCCL that ships with torch (nvidia-nccl wheel), or None: what OFA_NCCL_LIB should point to when the
+    process has no other NCCL."""
+    try:
+        import nvidia.nccl as pkg
+        for base in list(getattr(pkg, "__path__", [])):
+            cand = os.path.join(base, "lib", "libnccl.so.2")
+            if os.path.exists(cand):
+                return cand
+    except Exception:
+        pass
+    return None
+
+
+class NativeDataParallel:
+    """DataParallel's surface (enqueue / cancel / finish / wait) on the library's C++ communication side. The only thing it
+    needs from the host is the rendezvous: `exchange(id_bytes_or_None) -> id_bytes` hands rank 0's 128-byte id to every
+    rank (default: torch.distributed's object broadcast)."""
+
+    def __init__(self, mk, rank, world, exchange=None):
+        import ctypes as C
+        from . import capi
+        self.mk, self.C, self.capi, self.lib = mk, C, capi, mk.lib
+        self.buckets = mk.buckets()
+        if not self.buckets:
+            raise RuntimeError("the context was not created with ext_sync=1")
+        if "OFA_NCCL_LIB" not in os.environ and torch_nccl_library():
+            os.environ["OFA_NCCL_LIB"] = torch_nccl_library()
+        ident = None
+        if rank == 0:
+            buf = C.create_string_buffer(128)
+            if self.lib.ofa_dp_unique_id(buf) != capi.OK:
+                raise RuntimeError("ofa_dp_unique_id: " + self.lib.ofa_last_error(None).decode())
+            ident = buf.raw
+        if exchange is None:
+            import torch.distributed as dist
+            box = [ident]
+            dist.broadcast_object_list(box, src=0)
+            ident = box[0]
+        else:
+            ident = exchange(ident)
+        mk._chk(self.lib.ofa_dp_init(mk.h, C.c_char_p(ident), rank, world))
+
+    def enqueue(self, nsteps):
+        self.mk._chk(self.lib.ofa_dp_enqueue(self.mk.h, nsteps))
+
+    def cancel(self):
+        self.lib.ofa_dp_cancel(self.mk.h)
+
+    def finish(self, timeout_s=120.0):
+        return self.lib.ofa_dp_finish(self.mk.h, -1 if timeout_s is None else int(timeout_s * 1000)) == self.capi.OK
+
+    def wait(self, timeout_ms=600000, comm_timeout_s=120.0):
+        from .host import OfaError
+        st = self.capi.Status()
+        rc = self.lib.ofa_dp_wait(self.mk.h, timeout_ms, int(comm_timeout_s * 1000), self.C.byref(st))
+        if rc == self.capi.OK:
+            return
+        msg = self.lib.ofa_last_error(self.mk.h).decode()
+        if rc == self.capi.DEVICE_ABORT and "another rank" in msg:
+            raise DataParallelAborted(msg)
+        raise OfaError(rc, "timeout" if rc == self.capi.TIMEOUT and not msg else msg, st)
+
+    def close(self):
+        self.lib.ofa_dp_shutdown(self.mk.h)

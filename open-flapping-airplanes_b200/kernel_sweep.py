@@ -33,7 +33,7 @@ GEMMS = {
     "gemm_dln1": (1, 0, M, D, 3 * D), "gemm_head_dX": (0, 0, M, D, V), "gemm_dWqkv": (2, 4, D, 3 * D, M), "gemm_dWo": (2, 4, D, D, M),
     "gemm_dWup": (2, 4, D, FF, M), "gemm_dWdown": (2, 4, FF, D, M), "gemm_head_dW": (2, 4, V, D, M),
 }
-OTHERS = ["attn_fwd", "attn_bwd", "adamw", "cross_entropy", "ln_fwd", "ln_bwd", "embed_bwd_wte", "decode_148sm", "decode_24sm", "decode_attn", "sched_empty"]
+OTHERS = ["attn_fwd", "attn_bwd", "adamw", "cross_entropy", "ln_fwd", "ln_bwd", "embed_bwd_wte", "decode_148sm", "decode_24sm", "decode_attn", "sched_empty", "head_fused"]
 
 
 def peaks():
@@ -120,6 +120,28 @@ def run_ce(ofa, repeats):
     ms = ofa.run_phases(K.DTYPE_BF16, DIMS, [ofa.phase(K.TK_CE, [lg, tg, loss])], repeats=repeats) / repeats
     by = 2.0 * N * V * 2
     return {"kernel": "cross_entropy", "shape": [N, V], "ms": ms, "gbs": by / ms / 1e6, "bound": "hbm", "algorithmic_bytes": by}
+
+
+def run_head_fused(ofa, repeats):
+    """The fused LM head: the logits GEMM whose epilogue leaves per-tile softmax partials, then cross-entropy streaming the logits
+    once. Two records: the GEMM (tensor bound) and the cross-entropy task (HBM bound: reads and rewrites the bf16 logits). The
+    cross-entropy launch is timed on its own, after one launch has produced logits and partials; repeats work in place on what
+    the pass before left (the arithmetic is the same, the values are not meaningful)."""
+    K = ofa.capi
+    rng = np.random.default_rng(7)
+    N = B * T
+    x = rand_bf16(ofa, rng, (N, D), 1.0); W = rand_bf16(ofa, rng, (V, D), 0.05)
+    lg = ofa.DeviceBuffer((N, V), "bf16"); part = ofa.DeviceBuffer((N, V // 128, 2), np.float32)
+    tg = ofa.DeviceBuffer.from_host(rng.integers(0, V, N).astype(np.int32)); loss = ofa.DeviceBuffer((N,), np.float32)
+    ph = ofa.gemm_phase(1, K.EPI_LSE, N, V, D, x, D, W, D, lg, V)
+    ph.p[4] = part.ptr
+    ofa.run_phases(K.DTYPE_BF16, DIMS, [ph])
+    ms_g = ofa.run_phases(K.DTYPE_BF16, DIMS, [ph], repeats=repeats) / repeats
+    ms_c = ofa.run_phases(K.DTYPE_BF16, DIMS, [ofa.phase(K.TK_CE, [lg, tg, loss, part])], repeats=repeats) / repeats
+    flop = 2.0 * N * V * D
+    by = 2.0 * N * V * 2
+    return [{"kernel": "gemm_logits_lse", "shape": [N, V, D], "ms": ms_g, "tflops": flop / ms_g / 1e9, "bound": "tensor"},
+            {"kernel": "cross_entropy_stream", "shape": [N, V], "ms": ms_c, "gbs": by / ms_c / 1e6, "bound": "hbm", "algorithmic_bytes": by}]
 
 
 def run_ln(ofa, which, repeats):
@@ -267,6 +289,7 @@ def main():
         elif n == "decode_24sm": r = run_decode(ofa, 24, 261 * max(1, a.repeats))
         elif n == "decode_attn": r = run_decode_attn(ofa)
         elif n == "sched_empty": r = run_sched_empty(ofa, a.repeats)
+        elif n == "head_fused": r = run_head_fused(ofa, a.repeats)
         else: raise SystemExit(f"unknown case {n}")
         for rec in (r if isinstance(r, list) else [r]):
             rec["frac"] = (rec["tflops"] / tf) if rec["bound"] == "tensor" else (rec["gbs"] / hbm)

@@ -40,7 +40,8 @@ def main():
     mk = ofa.Megakernel(cfg)
     mk.load_weights(orc.flatten(ocfg, w0)); mk.set_tokens(tokens); mk.set_starts(starts.astype(np.uint32))
     log("context created, buckets %s" % (mk.buckets(),))
-    dp = ofa.dp.DataParallel(mk, dist)
+    # DP_SIDE=native: the library's own C++ queue and communicator; otherwise the process group of this script
+    dp = ofa.dp.NativeDataParallel(mk, rank, world) if os.environ.get("DP_SIDE") == "native" else ofa.dp.DataParallel(mk, dist)
     log("communication stream warmed up")
     for n in (2, nsteps - 2):                      # two launches: the flags restart, the optimizer state continues
         mk.launch(n); log(f"launched {n}"); dp.enqueue(n); log("enqueued"); dp.wait(60000, comm_timeout_s=60.0); log("kernel and communication done")
