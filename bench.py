@@ -169,7 +169,7 @@ def main():
                     help="ref_*: the same two workloads at the shapes the reference program is compiled for (vocab 100352 tied, context 512, batch 8), for a like-for-like line beside its own binary")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--repeats", type=int, default=0, help="timed K-step launches (0 = enough for more than a second of timed work, at least 5)")
-    ap.add_argument("--dp-side", choices=["native", "torch"], default="torch", help="N > 1: gradient all-reduce queued by the library's C++ side (its own NCCL communicator) or through torch.distributed")
+    ap.add_argument("--dp-side", choices=["native", "torch"], default="native", help="N > 1: gradient all-reduce queued by the library's C++ side (its own NCCL communicator) or through torch.distributed")
     ap.add_argument("--phase-table", action="store_true", help="also print the per-phase busy table to stderr")
     ap.add_argument("--cfg", action="append", default=[], metavar="FIELD=INT", help="override an integer field of ofa_config (experiments, e.g. gemm_nsub=2, head_dx_splitk=1); the run is then not the headline configuration")
     args = ap.parse_args()
