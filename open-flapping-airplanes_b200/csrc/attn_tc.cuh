@@ -199,23 +199,26 @@ __device__ __noinline__ void fwd_task(const Maps* mp, bf16* o, float* lse, int b
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      uint32_t s0[32], s1[32];
-      tmem_ld32_nw(tl + (c & 1) * 64, s0);
-      tmem_ld32_nw(tl + (c & 1) * 64 + 32, s1);
-      tmem_ld_wait();
-      tc_fence_before();
-      warp_arrive(bar(base, B_AFREE + (c & 1)));                               // S_j lives in registers now
+      // Two passes over the 64 scores of the row, each reading them from tensor memory (a read costs far less than keeping 64
+      // values live beside the packed probabilities: with both in registers the task spilled, and with the shared-memory
+      // carve-out at its maximum a spill goes to L2): pass 1 finds the maximum, pass 2 exponentiates half a row at a time.
+      const uint32_t ts = tl + (c & 1) * 64;
       const bool need_mask = __any_sync(0xffffffffu, k0 + KTILE - 1 > qg);       // warp-uniform: only tiles on the diagonal
       float mxa[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};             // four independent chains
-      if (!need_mask) {
+      {
+        uint32_t s0[32], s1[32];
+        tmem_ld32_nw(ts, s0);
+        tmem_ld32_nw(ts + 32, s1);
+        tmem_ld_wait();
+        if (!need_mask) {
 #pragma unroll
-        for (int x = 0; x < 32; x++) { mxa[x & 3] = fmaxf(mxa[x & 3], __uint_as_float(s0[x])); mxa[x & 3] = fmaxf(mxa[x & 3], __uint_as_float(s1[x])); }
-      } else {
+          for (int x = 0; x < 32; x++) { mxa[x & 3] = fmaxf(mxa[x & 3], __uint_as_float(s0[x])); mxa[x & 3] = fmaxf(mxa[x & 3], __uint_as_float(s1[x])); }
+        } else {
 #pragma unroll
-        for (int x = 0; x < 32; x++) {
-          if (k0 + x > qg) s0[x] = 0xff800000u;                                 // -inf: contributes neither to the maximum nor (2^-inf = 0) to the sum
-          if (k0 + 32 + x > qg) s1[x] = 0xff800000u;
-          mxa[x & 3] = fmaxf(mxa[x & 3], __uint_as_float(s0[x])); mxa[x & 3] = fmaxf(mxa[x & 3], __uint_as_float(s1[x]));
+          for (int x = 0; x < 32; x++) {
+            if (k0 + x <= qg) mxa[x & 3] = fmaxf(mxa[x & 3], __uint_as_float(s0[x]));   // masked scores contribute neither to the maximum nor to the sum
+            if (k0 + 32 + x <= qg) mxa[x & 3] = fmaxf(mxa[x & 3], __uint_as_float(s1[x]));
+          }
         }
       }
       const float mx = fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3]));
@@ -245,22 +248,23 @@ __device__ __noinline__ void fwd_task(const Maps* mp, bf16* o, float* lse, int b
       float rsa[4] = {0.f, 0.f, 0.f, 0.f};
       unsigned char* tile = smem + 65536 + (c & 1) * 16384;
       const float nm = -m;
-      {
-        uint32_t pk[16];
+#pragma unroll
+      for (int hf = 0; hf < 2; hf++) {
+        uint32_t sv[32], pk[16];
+        tmem_ld32_nw(ts + hf * 32, sv);
+        tmem_ld_wait();
+        if (hf == 1) { tc_fence_before(); warp_arrive(bar(base, B_AFREE + (c & 1))); }   // S_j has been read for the last time
+        if (need_mask) {
+#pragma unroll
+          for (int x = 0; x < 32; x++) if (k0 + hf * 32 + x > qg) sv[x] = 0xff800000u;   // -inf: 2^-inf = 0
+        }
 #pragma unroll
         for (int x = 0; x < 32; x += 2) {
-          const float p0 = ex2(fmaf(__uint_as_float(s0[x]), SCALE_LOG2, nm)), p1 = ex2(fmaf(__uint_as_float(s0[x + 1]), SCALE_LOG2, nm));
+          const float p0 = ex2(fmaf(__uint_as_float(sv[x]), SCALE_LOG2, nm)), p1 = ex2(fmaf(__uint_as_float(sv[x + 1]), SCALE_LOG2, nm));
           rsa[(x >> 1) & 3] += p0 + p1;
           pk[x >> 1] = pack2(p0, p1);
         }
-        store_chunks(tile, r, 0, pk);
-#pragma unroll
-        for (int x = 0; x < 32; x += 2) {
-          const float p0 = ex2(fmaf(__uint_as_float(s1[x]), SCALE_LOG2, nm)), p1 = ex2(fmaf(__uint_as_float(s1[x + 1]), SCALE_LOG2, nm));
-          rsa[(x >> 1) & 3] += p0 + p1;
-          pk[x >> 1] = pack2(p0, p1);
-        }
-        store_chunks(tile, r, 4, pk);
+        store_chunks(tile, r, hf * 4, pk);
       }
       const float rs = (rsa[0] + rsa[1]) + (rsa[2] + rsa[3]);
       l += rs;
