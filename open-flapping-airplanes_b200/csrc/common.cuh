@@ -108,6 +108,10 @@ __device__ __forceinline__ uint4 pack8(const float* f) {
   for (int i = 0; i < 4; i++) p[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
   return u;
 }
+__device__ __forceinline__ uint32_t pack2f(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
 // load / store `Vec<T>::N` consecutive elements (16 bytes) as floats
 __device__ __forceinline__ void ldv(const bf16* p, float* f) { unpack8(*reinterpret_cast<const uint4*>(p), f); }
 __device__ __forceinline__ void ldv(const float* p, float* f) { float4 v = *reinterpret_cast<const float4*>(p); f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w; }

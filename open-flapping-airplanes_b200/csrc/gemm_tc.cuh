@@ -154,6 +154,7 @@ __device__ __forceinline__ void gemm_tc_task(const GemmArgs& g, int tiles_m, int
   using CF = Cfg<BN>;
   constexpr bool A_MN = (LAYOUT == GL_TN), B_MN = (LAYOUT != GL_NT);
   constexpr bool HAS_AUX_IN = (EPI == GE_RES || EPI == GE_DGELU || EPI == GE_DR);
+  constexpr bool BF16_STAGED = (EPI == GE_STORE || EPI == GE_GELU || EPI == GE_LSE || EPI == GE_DR);   // epilogues whose stored value is the rounded accumulator
   constexpr uint32_t IDESC = umma_idesc(A_MN, B_MN, BM, BN);
   constexpr int STAGES = CF::STAGES, W = CF::W;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -237,7 +238,14 @@ __device__ __forceinline__ void gemm_tc_task(const GemmArgs& g, int tiles_m, int
         // Epilogues that read `aux` (residual, pre-activation) fetch this thread's 16 row segments of the 128 columns BEFORE
         // waiting for the accumulator, so the loads travel while the MMAs run instead of being 16 dependent round trips.
         uint4 auxr[HAS_AUX_IN ? 16 : 1];
-        if constexpr (HAS_AUX_IN) {
+        if constexpr (EPI == GE_DR) {                    // layout of the bf16-staged pass below: row = it*4 + lane/8, 8 columns at (lane%8)*8
+          const bf16* aux = reinterpret_cast<const bf16*>(g.aux);
+#pragma unroll
+          for (int cp = 0; cp < 2; cp++)
+#pragma unroll
+            for (int it = 0; it < 8; it++)
+              auxr[cp * 8 + it] = *reinterpret_cast<const uint4*>(aux + (size_t)(m0 + e * 32 + it * 4 + (lane >> 3)) * g.ldaux + n0 + half * 128 + cp * 64 + (lane & 7) * 8);
+        } else if constexpr (HAS_AUX_IN) {
           const bf16* aux = reinterpret_cast<const bf16*>(g.aux);
 #pragma unroll
           for (int c = 0; c < 4; c++)
@@ -251,13 +259,101 @@ __device__ __forceinline__ void gemm_tc_task(const GemmArgs& g, int tiles_m, int
           if (!ok) break;
           tc_fence_after();
         }
-        // GE_LSE: running maximum (log2 domain) and sum of 2^(x - max) of this lane's share of four rows, over the tile's 128 columns
-        float lm[EPI == GE_LSE ? 4 : 1], ls[EPI == GE_LSE ? 4 : 1];
+        if constexpr (BF16_STAGED) {
+          // The stored value is the bf16 rounding of the accumulator itself, so the accumulator is rounded BEFORE the transpose:
+          // the thread that owns row `lane` packs 64 columns into eight 16-byte chunks of a 32 x 128 B tile (chunk j at
+          // position j ^ (lane & 7)), and the warp reads it back as 4 rows x 128 B per instruction - whole lines for the
+          // stores, half the shared-memory traffic of an fp32 transpose (the pipeline's own traffic nearly saturates it).
+          unsigned char* sb = reinterpret_cast<unsigned char*>(stg);
+          const int sub = lane >> 3, ch = lane & 7;
+          float lm[EPI == GE_LSE ? 8 : 1], ls[EPI == GE_LSE ? 8 : 1];   // GE_LSE: running maximum (log2 domain) and sum of 2^(x - max) per row slot
 #pragma unroll
-        for (int i = 0; i < (EPI == GE_LSE ? 4 : 1); i++) { lm[i] = -INFINITY; ls[i] = 0.f; }
-        float drp[EPI == GE_DR ? 8 : 1];                 // GE_DR: this lane's partial row sums, [row slot it][head of the tile]
+          for (int i = 0; i < (EPI == GE_LSE ? 8 : 1); i++) { lm[i] = -INFINITY; ls[i] = 0.f; }
 #pragma unroll
-        for (int i = 0; i < (EPI == GE_DR ? 8 : 1); i++) drp[i] = 0.f;
+          for (int cp = 0; cp < 2; cp++) {                 // 64 columns at a time
+#pragma unroll
+            for (int hc = 0; hc < 2; hc++) {
+              uint32_t r[32];
+              tmem_ld32(gp.tmem_base + ((uint32_t)(e * 32) << 16) + (uint32_t)(b * BN + half * 128 + cp * 64 + hc * 32), r);
+              if (half == BN / 128 - 1 && cp == 1 && hc == 1) {    // all TMEM reads of this accumulator are done: hand it back early
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_acce<BN>(base, b));
+              }
+#pragma unroll
+              for (int q = 0; q < 4; q++) {
+                uint4 v;
+                v.x = pack2f(__uint_as_float(r[8 * q]), __uint_as_float(r[8 * q + 1])); v.y = pack2f(__uint_as_float(r[8 * q + 2]), __uint_as_float(r[8 * q + 3]));
+                v.z = pack2f(__uint_as_float(r[8 * q + 4]), __uint_as_float(r[8 * q + 5])); v.w = pack2f(__uint_as_float(r[8 * q + 6]), __uint_as_float(r[8 * q + 7]));
+                *reinterpret_cast<uint4*>(sb + lane * 128 + (((hc * 4 + q) ^ (lane & 7)) << 4)) = v;
+              }
+            }
+            __syncwarp();
+            float drs[EPI == GE_DR ? 8 : 1];
+#pragma unroll
+            for (int it = 0; it < 8; it++) {
+              const int rr = it * 4 + sub;
+              const uint4 out = *reinterpret_cast<const uint4*>(sb + rr * 128 + ((ch ^ (rr & 7)) << 4));
+              const size_t row = (size_t)(m0 + e * 32 + rr);
+              const int col = n0 + half * 128 + cp * 64 + ch * 8;
+              if constexpr (EPI == GE_GELU) {
+                *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(g.aux) + row * g.ldaux + col) = out;   // bf16-rounded pre-activation is what backward sees
+                float pv[8]; unpack8(out, pv);
+#pragma unroll
+                for (int i = 0; i < 8; i++) pv[i] = gelu_fwd<true>(pv[i]);
+                *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(g.C) + row * g.ldc + col) = pack8(pv);
+              } else {
+                *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(g.C) + row * g.ldc + col) = out;
+              }
+              if constexpr (EPI == GE_LSE) {
+                float y[8]; unpack8(out, y);               // the STORED values: the partials describe exactly what cross-entropy will read
+                float gm = y[0];
+#pragma unroll
+                for (int i = 1; i < 8; i++) gm = fmaxf(gm, y[i]);
+                gm *= 1.4426950408889634f;
+                if (gm > lm[it]) { ls[it] *= ex2_approx(lm[it] - gm); lm[it] = gm; }
+                float s2 = 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; i += 2) { ls[it] += ex2_approx(fmaf(y[i], 1.4426950408889634f, -lm[it])); s2 += ex2_approx(fmaf(y[i + 1], 1.4426950408889634f, -lm[it])); }
+                ls[it] += s2;
+              }
+              if constexpr (EPI == GE_DR) {
+                float c8[8], o8[8]; unpack8(out, c8); unpack8(auxr[cp * 8 + it], o8);
+                float sdot = 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; i++) sdot = fmaf(c8[i], o8[i], sdot);
+                drs[it] = sdot;
+              }
+            }
+            if constexpr (EPI == GE_DR) {                  // one pass = the 64 columns of one head; a row's share sits in 8 lanes
+              // the 128 rows of a tile belong to one sequence (the context length is a multiple of 128): one division per tile
+              const int bseq = m0 / g.dr_T, t0 = m0 - bseq * g.dr_T + e * 32 + sub;
+              float* drow = g.dr + ((size_t)bseq * g.dr_H + (n0 + half * 128) / 64 + cp) * g.dr_T + t0;
+#pragma unroll
+              for (int it = 0; it < 8; it++) {
+                float v = drs[it];
+                v += __shfl_xor_sync(0xffffffffu, v, 1); v += __shfl_xor_sync(0xffffffffu, v, 2); v += __shfl_xor_sync(0xffffffffu, v, 4);
+                if (ch == 0) drow[it * 4] = v;
+              }
+            }
+            __syncwarp();
+          }
+          if constexpr (EPI == GE_LSE) {                   // a row's 128 columns sit in 8 lanes: merge their (max, sum) pairs, same result in all eight
+            float2* part = reinterpret_cast<float2*>(g.dr) + (size_t)(m0 + e * 32 + sub) * (g.N / 128) + (n0 + half * 128) / 128;
+#pragma unroll
+            for (int it = 0; it < 8; it++) {
+              float m_ = lm[it], s_ = ls[it];
+#pragma unroll
+              for (int o = 1; o <= 4; o <<= 1) {
+                const float mo = __shfl_xor_sync(0xffffffffu, m_, o), so = __shfl_xor_sync(0xffffffffu, s_, o);
+                const float mn = fmaxf(m_, mo);
+                s_ = s_ * ex2_approx(m_ - mn) + so * ex2_approx(mo - mn);
+                m_ = mn;
+              }
+              if (ch == 0) part[(size_t)it * 4 * (g.N / 128)] = make_float2(m_, s_);
+            }
+          }
+        } else {
 #pragma unroll
         for (int c = 0; c < 4; c++) {
           uint32_t r[32];
@@ -280,51 +376,10 @@ __device__ __forceinline__ void gemm_tc_task(const GemmArgs& g, int tiles_m, int
             const float4 a0 = *reinterpret_cast<const float4*>(stg + rr * 32 + (((2 * cg) ^ (rr & 7)) << 2));
             const float4 a1 = *reinterpret_cast<const float4*>(stg + rr * 32 + (((2 * cg + 1) ^ (rr & 7)) << 2));
             const float acc[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-            if constexpr (EPI == GE_LSE) {
-              const uint4 out = pack8(acc);
-              *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(g.C) + (size_t)(m0 + e * 32 + rr) * g.ldc + n0 + half * 128 + c * 32 + cg * 8) = out;
-              float y[8]; unpack8(out, y);             // the STORED values: the partials describe exactly what cross-entropy will read
-              float gm = y[0];
-#pragma unroll
-              for (int i = 1; i < 8; i++) gm = fmaxf(gm, y[i]);
-              gm *= 1.4426950408889634f;
-              if (gm > lm[it]) { ls[it] *= ex2_approx(lm[it] - gm); lm[it] = gm; }
-              float s2 = 0.f;
-#pragma unroll
-              for (int i = 0; i < 8; i += 2) { ls[it] += ex2_approx(fmaf(y[i], 1.4426950408889634f, -lm[it])); s2 += ex2_approx(fmaf(y[i + 1], 1.4426950408889634f, -lm[it])); }
-              ls[it] += s2;
-            } else {
-              const float part = epi_store8<EPI>(g, (size_t)(m0 + e * 32 + rr), n0 + half * 128 + c * 32 + cg * 8, acc, auxr[HAS_AUX_IN ? c * 4 + it : 0]);
-              if constexpr (EPI == GE_DR) drp[it * 2 + (c >> 1)] += part;
-            }
+            epi_store8<EPI>(g, (size_t)(m0 + e * 32 + rr), n0 + half * 128 + c * 32 + cg * 8, acc, auxr[HAS_AUX_IN ? c * 4 + it : 0]);
           }
           __syncwarp();
         }
-        if constexpr (EPI == GE_LSE) {                   // a row's 128 columns sit in the 4 lanes of a quad: merge their (max, sum) pairs, same result in all four
-          float2* part = reinterpret_cast<float2*>(g.dr) + (size_t)(m0 + e * 32 + (lane >> 2)) * (g.N / 128) + (n0 + half * 128) / 128;
-#pragma unroll
-          for (int it = 0; it < 4; it++) {
-            float m_ = lm[it], s_ = ls[it];
-#pragma unroll
-            for (int o = 1; o <= 2; o <<= 1) {
-              const float mo = __shfl_xor_sync(0xffffffffu, m_, o), so = __shfl_xor_sync(0xffffffffu, s_, o);
-              const float mn = fmaxf(m_, mo);
-              s_ = s_ * ex2_approx(m_ - mn) + so * ex2_approx(mo - mn);
-              m_ = mn;
-            }
-            if (cg == 0) part[(size_t)it * 8 * (g.N / 128)] = make_float2(m_, s_);
-          }
-        }
-        if constexpr (EPI == GE_DR) {                    // a row's 64 columns of a head sit in the 4 lanes of a quad (2 chunks each)
-          // the 128 rows of a tile belong to one sequence (the context length is a multiple of 128): one division per tile
-          const int bseq = m0 / g.dr_T, t0 = m0 - bseq * g.dr_T + e * 32 + (lane >> 2);
-          float* drow = g.dr + ((size_t)bseq * g.dr_H + (n0 + half * 128) / 64) * g.dr_T + t0;
-#pragma unroll
-          for (int i = 0; i < 8; i++) {
-            float v = drp[i];
-            v += __shfl_xor_sync(0xffffffffu, v, 1); v += __shfl_xor_sync(0xffffffffu, v, 2);
-            if (cg == 0) drow[(size_t)(i & 1) * g.dr_T + (i >> 1) * 8] = v;
-          }
         }
       }
     }
