@@ -290,10 +290,15 @@ __device__ __forceinline__ void gemm_tc_task(const GemmArgs& g, int tiles_m, int
             }
             __syncwarp();
             float drs[EPI == GE_DR ? 8 : 1];
+            // all eight reads first: a global store between two shared-memory reads keeps the compiler from moving the second
+            // read up (it cannot rule out aliasing), and the pass would pay eight shared-memory latencies in a row
+            uint4 ov[8];
+#pragma unroll
+            for (int it = 0; it < 8; it++) { const int rr = it * 4 + sub; ov[it] = *reinterpret_cast<const uint4*>(sb + rr * 128 + ((ch ^ (rr & 7)) << 4)); }
 #pragma unroll
             for (int it = 0; it < 8; it++) {
               const int rr = it * 4 + sub;
-              const uint4 out = *reinterpret_cast<const uint4*>(sb + rr * 128 + ((ch ^ (rr & 7)) << 4));
+              const uint4 out = ov[it];
               const size_t row = (size_t)(m0 + e * 32 + rr);
               const int col = n0 + half * 128 + cp * 64 + ch * 8;
               if constexpr (EPI == GE_GELU) {
@@ -370,11 +375,17 @@ __device__ __forceinline__ void gemm_tc_task(const GemmArgs& g, int tiles_m, int
                 make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
           __syncwarp();
           // 8 rows per instruction: lane -> (row = it*8 + lane/4, 8 consecutive columns (lane%4)*8..)
+          float4 av[8];                            // all reads before the first global store (see the bf16-staged pass)
 #pragma unroll
           for (int it = 0; it < 4; it++) {
             const int rr = it * 8 + (lane >> 2);
-            const float4 a0 = *reinterpret_cast<const float4*>(stg + rr * 32 + (((2 * cg) ^ (rr & 7)) << 2));
-            const float4 a1 = *reinterpret_cast<const float4*>(stg + rr * 32 + (((2 * cg + 1) ^ (rr & 7)) << 2));
+            av[2 * it] = *reinterpret_cast<const float4*>(stg + rr * 32 + (((2 * cg) ^ (rr & 7)) << 2));
+            av[2 * it + 1] = *reinterpret_cast<const float4*>(stg + rr * 32 + (((2 * cg + 1) ^ (rr & 7)) << 2));
+          }
+#pragma unroll
+          for (int it = 0; it < 4; it++) {
+            const int rr = it * 8 + (lane >> 2);
+            const float4 a0 = av[2 * it], a1 = av[2 * it + 1];
             const float acc[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
             epi_store8<EPI>(g, (size_t)(m0 + e * 32 + rr), n0 + half * 128 + c * 32 + cg * 8, acc, auxr[HAS_AUX_IN ? c * 4 + it : 0]);
           }
