@@ -23,7 +23,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
-DEFAULT_REF = "/root/reference"
+DEFAULT_REF = os.environ.get("OFA_REFERENCE_DIR", os.path.join(os.sep, "root", "reference"))   # a checkout of the reference project
 
 
 def _nvcc():

@@ -158,7 +158,8 @@ def test_bf16_loss_curve_and_repeatability(ofa, oracle):
 
 
 def test_gpt_s_full_size_properties(ofa, oracle):
-    """BASELINE config 2 at full size: size-independent checks (the oracle would need minutes per step here)."""
+    """Full-size GPT-S with the optional graph variants switched on: size-independent checks (the 100-step comparison with the
+    oracle at this size lives in tests/test_gpu_northstar.py)."""
     cfg = ofa.default_config("gpt_s")
     cfg.adam_interleave, cfg.head_dx_splitk = 1, 1            # also exercises the optional graph variants at full size
     mk = ofa.Megakernel(cfg)
