@@ -388,12 +388,14 @@ bool build_train_graph(ofa_ctx* c) {
     prevdeps.push_back(pv);
   };
   auto mk = [&](int kind, int ntasks) { PhaseDesc d; memset(&d, 0, sizeof d); d.kind = kind; d.ntasks = ntasks; return d; };
+  // wide = 1: 128 x 256 tiles where the width allows (a long K and more tiles than blocks: only the LM head's weight gradient)
   auto mkgemm = [&](int layout, int epi, const void* A, int lda, const void* B, int ldb, void* Cc, int ldc, void* aux, int ldaux,
-                    int M, int Nn, int K, int accumulate) {
+                    int M, int Nn, int K, int accumulate, int wide = 0) {
     PhaseDesc d = mk(TK_GEMM, 0); d.layout = layout; d.epi = epi;
     d.g.A = A; d.g.B = B; d.g.C = Cc; d.g.aux = aux; d.g.M = M; d.g.N = Nn; d.g.K = K; d.g.lda = lda; d.g.ldb = ldb; d.g.ldc = ldc; d.g.ldaux = ldaux;
     d.g.accumulate = accumulate;
-    if (bf) { std::string e; if (!prepare_gemm_bf16(d, c->ar, cfg.gemm_nsub, c->C.train_sms > 0 ? 2 * c->C.train_sms : c->nblocks, e)) { ok = false; err = e; } }   // waves are counted over the blocks that train
+    const int nsub_cfg = (wide && cfg.gemm_nsub == 0 && !getenv("OFA_B200_HEAD_DW_128")) ? 2000 : cfg.gemm_nsub;
+    if (bf) { std::string e; if (!prepare_gemm_bf16(d, c->ar, nsub_cfg, c->C.train_sms > 0 ? 2 * c->C.train_sms : c->nblocks, e)) { ok = false; err = e; } }   // waves are counted over the blocks that train
     else prepare_gemm_f32(d);
     return d;
   };
@@ -615,7 +617,7 @@ bool build_train_graph(ofa_ctx* c) {
         addp("head dX", dsum, parts, {});
       }
     }
-    addb("head dW", mkgemm(GL_TN, wepi, logits, V, lnf, D, G(lay.head), D, nullptr, 0, V, D, N, 0), {"cross-entropy"}, {});
+    addb("head dW", mkgemm(GL_TN, wepi, logits, V, lnf, D, G(lay.head), D, nullptr, 0, V, D, N, 0, /*wide=*/1), {"cross-entropy"}, {});
     if (trickle_n && !lay.tied) { AdamItem it; it.name = "adamw head"; it.off = lay.head; it.n = V * D; it.deps = {"head dW", "head dX"}; adam_q.push_back(it); }
     if (ext && !lay.tied) signal(0);
     { PhaseDesc d = mk(TK_LN_BWD, rows16); d.p[0] = dxs[L]; d.p[1] = dgpf; d.p[2] = dxf; d.p[3] = xs[L]; d.p[4] = meanf; d.p[5] = rstdf; d.p[6] = Wact + lay.gf; d.p[7] = nullptr;
