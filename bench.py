@@ -215,6 +215,7 @@ def main():
     elif world > 1:
         cfg.reserved_sms = 8
     dp = None
+    dp_side = args.dp_side
     if world > 1:
         cfg.dp_world, cfg.grad_bf16, cfg.ext_sync = world, 1, 1
     cfg.sched_profile = 1 if args.phase_table else 0    # the in-kernel time tables are only read by --phase-table
@@ -230,7 +231,20 @@ def main():
     mk.set_tokens(tokens)
     if world > 1:
         # NCCL gradient all-reduce ordered by device flags
-        dp = ofa.dp.NativeDataParallel(mk, rank, world) if args.dp_side == "native" else ofa.dp.DataParallel(mk, dist)
+        if dp_side == "native":
+            try:
+                dp = ofa.dp.NativeDataParallel(mk, rank, world)
+            except Exception as e:                         # e.g. no NCCL library found by the C++ side: every rank takes the same branch below
+                print(f"[rank {rank}] the library's own communication side is unavailable ({e}); using torch.distributed", file=sys.stderr)
+                dp = None
+            ok_all = torch.tensor([1 if dp is not None else 0], device="cuda", dtype=torch.int32)
+            dist.all_reduce(ok_all, op=dist.ReduceOp.MIN)
+            if int(ok_all.item()) == 0:
+                if dp is not None:
+                    dp.close()
+                dp, dp_side = None, "torch"
+        if dp is None:
+            dp = ofa.dp.DataParallel(mk, dist)
 
     def barrier():
         torch.cuda.synchronize()
@@ -303,7 +317,7 @@ def main():
             "config": {"workload": ((f"gpt_s at the reference program's shapes V={V} tied D=768 L=12 H=12 T={T} B={B} (4096 tok/step/GPU), " if ref_shapes else "gpt_s V=50304 untied D=768 L=12 H=12 T=1024 B=4 (4096 tok/step/GPU), ") +
                                     ("116 train / 24 serve / 8 reserved SMs with concurrent batch-1 greedy decode (6-token prompt, 256 generated, repeating)" if split else "training only on all SMs")),
                        "parallelism": f"dp{world}" + (", ranks > 0 train on 116 SMs and leave the 24 serving SMs idle (one serving replica, on rank 0)" if (world > 1 and split) else ""), "l2": "working set per step (>2 GB) exceeds the 126 MB L2; no flush needed",
-                       "projected_4000_steps_s": ms / K * 4000 / 1e3, **({"overrides": args.cfg} if args.cfg else {})},
+                       "projected_4000_steps_s": ms / K * 4000 / 1e3, **({"allreduce_queue": ("library (C++, own NCCL communicator)" if dp_side == "native" else "torch.distributed")} if world > 1 else {}), **({"overrides": args.cfg} if args.cfg else {})},
             "decode_tok_s": dec_tok_s, "final_loss": float(losses[-1]), "first_loss": float(losses[0]),
             "e2e": {"value": world * TOKENS_PER_STEP * K / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": int(window.nbytes / K + starts.nbytes / K), "d2h_bytes_per_step": 4},
             "gpu_launches": 2 if split else 1,   # the persistent kernel, and with the decoder its one-block residual rebuild before it

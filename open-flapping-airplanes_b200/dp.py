@@ -292,19 +292,22 @@ class NativeDataParallel:
             raise RuntimeError("the context was not created with ext_sync=1")
         if "OFA_NCCL_LIB" not in os.environ and torch_nccl_library():
             os.environ["OFA_NCCL_LIB"] = torch_nccl_library()
-        ident = None
+        ident, why = None, ""
         if rank == 0:
             buf = C.create_string_buffer(128)
-            if self.lib.ofa_dp_unique_id(buf) != capi.OK:
-                raise RuntimeError("ofa_dp_unique_id: " + self.lib.ofa_last_error(None).decode())
-            ident = buf.raw
+            if self.lib.ofa_dp_unique_id(buf) == capi.OK:
+                ident = buf.raw
+            else:
+                why = self.lib.ofa_last_error(None).decode()      # the other ranks still get their answer below: nobody waits for good
         if exchange is None:
             import torch.distributed as dist
-            box = [ident]
+            box = [ident, why]
             dist.broadcast_object_list(box, src=0)
-            ident = box[0]
+            ident, why = box
         else:
             ident = exchange(ident)
+        if ident is None:
+            raise RuntimeError("ofa_dp_unique_id failed on rank 0: " + why)
         mk._chk(self.lib.ofa_dp_init(mk.h, C.c_char_p(ident), rank, world))
 
     def enqueue(self, nsteps):
