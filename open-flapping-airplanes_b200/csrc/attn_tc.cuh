@@ -132,7 +132,7 @@ __device__ __forceinline__ void warp_arrive(uint32_t b) { __syncwarp(); if ((thr
 // same softmax; after the first tiles of a row the rescale is rare and the step is one pass over S.
 constexpr float RESCALE_LOG2 = 8.f;
 __device__ __noinline__ void fwd_task(const Maps* mp, bf16* o, float* lse, int b, int h, int qt, int T, int H, unsigned char* smem,
-                                      AttnPipe& ap, uint32_t tmem, DevStatus* st, int phase_id, int task) {
+                                      AttnPipe& ap, uint32_t tmem, DevStatus* st, int phase_id, int task, const EarlyTicket& et) {
   const int D = H * DH;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const uint32_t base = smem_u32(smem);
@@ -154,6 +154,7 @@ __device__ __noinline__ void fwd_task(const Maps* mp, bf16* o, float* lse, int b
         tma_load_2d(sSt + s * 16384, &mp->qkv64, full, D + h * DH, nrow0 + j * KTILE);
         tma_load_2d(sSt + s * 16384 + 8192, &mp->qkv64, full, 2 * D + h * DH, nrow0 + j * KTILE);
       }
+      if (!aborted(st)) take_early_ticket(et);                               // the last copy of the task is on its way
       if (aborted(st)) drain(base, B_STFULL, ap.stages, sc, NST);
     }
   } else if (warp == 1) {
@@ -301,7 +302,7 @@ __device__ __noinline__ void fwd_task(const Maps* mp, bf16* o, float* lse, int b
 // ---------------------------------------------------------------------------------------------- backward: dK, dV
 // Task (b, h, kt): 128 key rows k0 = kt*128; walks query blocks of 64 rows from the diagonal to the end of the sequence.
 __device__ __noinline__ void bwd_dkdv_task(const Maps* mp, const float* lse, const float* Dr, bf16* dqkv, int b, int h, int kt, int T, int H,
-                                           unsigned char* smem, AttnPipe& ap, uint32_t tmem, DevStatus* st, int phase_id, int task) {
+                                           unsigned char* smem, AttnPipe& ap, uint32_t tmem, DevStatus* st, int phase_id, int task, const EarlyTicket& et) {
   const int D = H * DH, ld = 3 * D;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const uint32_t base = smem_u32(smem);
@@ -329,6 +330,7 @@ __device__ __noinline__ void bwd_dkdv_task(const Maps* mp, const float* lse, con
         bulk_1d(sStat + s * 512, Lg + (i0 + i) * KTILE, 256, full);
         bulk_1d(sStat + s * 512 + 256, Dg + (i0 + i) * KTILE, 256, full);
       }
+      if (!aborted(st)) take_early_ticket(et);
       if (aborted(st)) drain(base, B_ST2FULL, st0, sc, NST);
     }
   } else if (warp == 1) {
@@ -440,7 +442,7 @@ __device__ __noinline__ void bwd_dkdv_task(const Maps* mp, const float* lse, con
 // ---------------------------------------------------------------------------------------------- backward: dQ
 // Task (b, h, qt): 128 query rows; walks key blocks of 64 rows from 0 to the diagonal.
 __device__ __noinline__ void bwd_dq_task(const Maps* mp, const float* lse, const float* Dr, bf16* dqkv, int b, int h, int qt, int T, int H,
-                                         unsigned char* smem, AttnPipe& ap, uint32_t tmem, DevStatus* st, int phase_id, int task) {
+                                         unsigned char* smem, AttnPipe& ap, uint32_t tmem, DevStatus* st, int phase_id, int task, const EarlyTicket& et) {
   const int D = H * DH, ld = 3 * D;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const uint32_t base = smem_u32(smem);
@@ -463,6 +465,7 @@ __device__ __noinline__ void bwd_dq_task(const Maps* mp, const float* lse, const
         tma_load_2d(sSt + s * 16384, &mp->qkv64, full, D + h * DH, nrow0 + j * KTILE);
         tma_load_2d(sSt + s * 16384 + 8192, &mp->qkv64, full, 2 * D + h * DH, nrow0 + j * KTILE);
       }
+      if (!aborted(st)) take_early_ticket(et);                               // the last copy of the task is on its way
       if (aborted(st)) drain(base, B_STFULL, ap.stages, sc, NST);
     }
   } else if (warp == 1) {

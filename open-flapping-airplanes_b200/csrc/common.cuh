@@ -179,6 +179,12 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const D
   return mbar_wait_slow(bar, parity, st);
 }
 
+// The next ticket of the block's job, taken by thread 0 from inside a task once its own part of the task is over (the copy
+// producer after its last copy): the fetch-add's round trip then runs beside the rest of the task instead of after it.
+// slot: a word of the control area, 0 = nothing taken, else ticket + 1. counter == nullptr: not offered (serving job).
+struct EarlyTicket { unsigned* counter; volatile int* slot; };
+__device__ __forceinline__ void take_early_ticket(const EarlyTicket& e) { if (e.counter) *e.slot = (int)(atomicAdd(e.counter, 1u) + 1u); }
+
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
 // 2-D tiled TMA load (no multicast), completion counted in bytes on `bar`. c0 = innermost coordinate (elements).
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, uint32_t bar, int c0, int c1) {

@@ -150,7 +150,7 @@ __device__ __forceinline__ float epi_store8(const GemmArgs& g, size_t row, int c
 // task index -> (tile_m, first tile_n): consecutive tasks walk down M first so that neighbouring blocks share the B strip.
 template <int LAYOUT, int EPI, int BN>
 __device__ __forceinline__ void gemm_tc_task(const GemmArgs& g, int tiles_m, int task, unsigned char* smem, GemmPipe& gp,
-                                             DevStatus* st, int phase_id) {
+                                             DevStatus* st, int phase_id, const EarlyTicket& et) {
   using CF = Cfg<BN>;
   constexpr bool A_MN = (LAYOUT == GL_TN), B_MN = (LAYOUT != GL_NT);
   constexpr bool HAS_AUX_IN = (EPI == GE_RES || EPI == GE_DGELU || EPI == GE_DR);
@@ -191,6 +191,7 @@ __device__ __forceinline__ void gemm_tc_task(const GemmArgs& g, int tiles_m, int
           }
         }
       }
+      if (ok) take_early_ticket(et);     // every copy of the task is on its way: this thread has nothing left to do but the closing barrier
       if (aborted(st)) {       // giving up: wait (bounded) until the copies this task issued into our shared memory have landed
         const uint32_t issued = sc - gp.stage_count[W];
         for (uint32_t i = 0; i < issued && i < (uint32_t)STAGES; i++) {
@@ -401,23 +402,23 @@ __device__ __forceinline__ void gemm_tc_task(const GemmArgs& g, int tiles_m, int
 }
 
 template <int LAYOUT, int EPI>
-__device__ __forceinline__ void dispatch_bn(const PhaseDesc& d, int task, unsigned char* smem, GemmPipe& gp, DevStatus* st, int phase_id) {
-  if (d.g.bn == 256) gemm_tc_task<LAYOUT, EPI, 256>(d.g, d.tiles_m, task, smem, gp, st, phase_id);
-  else gemm_tc_task<LAYOUT, EPI, 128>(d.g, d.tiles_m, task, smem, gp, st, phase_id);
+__device__ __forceinline__ void dispatch_bn(const PhaseDesc& d, int task, unsigned char* smem, GemmPipe& gp, DevStatus* st, int phase_id, const EarlyTicket& et) {
+  if (d.g.bn == 256) gemm_tc_task<LAYOUT, EPI, 256>(d.g, d.tiles_m, task, smem, gp, st, phase_id, et);
+  else gemm_tc_task<LAYOUT, EPI, 128>(d.g, d.tiles_m, task, smem, gp, st, phase_id, et);
 }
 // run-time dispatch over the (layout, epilogue) pairs the training graph uses
-__device__ __noinline__ void run(const PhaseDesc& d, int task, unsigned char* smem, GemmPipe& gp, DevStatus* st, int phase_id) {
+__device__ __noinline__ void run(const PhaseDesc& d, int task, unsigned char* smem, GemmPipe& gp, DevStatus* st, int phase_id, const EarlyTicket& et) {
   switch (d.layout * 8 + d.epi) {
-    case GL_NN * 8 + GE_STORE: dispatch_bn<GL_NN, GE_STORE>(d, task, smem, gp, st, phase_id); break;
-    case GL_NN * 8 + GE_RES:   dispatch_bn<GL_NN, GE_RES>(d, task, smem, gp, st, phase_id); break;
-    case GL_NN * 8 + GE_GELU:  dispatch_bn<GL_NN, GE_GELU>(d, task, smem, gp, st, phase_id); break;
-    case GL_NN * 8 + GE_F32:   dispatch_bn<GL_NN, GE_F32>(d, task, smem, gp, st, phase_id); break;      // split-K partial products
-    case GL_NT * 8 + GE_STORE: dispatch_bn<GL_NT, GE_STORE>(d, task, smem, gp, st, phase_id); break;
-    case GL_NT * 8 + GE_DGELU: dispatch_bn<GL_NT, GE_DGELU>(d, task, smem, gp, st, phase_id); break;
-    case GL_NT * 8 + GE_DR:    gemm_tc_task<GL_NT, GE_DR, 128>(d.g, d.tiles_m, task, smem, gp, st, phase_id); break;
-    case GL_NT * 8 + GE_LSE:   gemm_tc_task<GL_NT, GE_LSE, 128>(d.g, d.tiles_m, task, smem, gp, st, phase_id); break;
-    case GL_TN * 8 + GE_F32:   dispatch_bn<GL_TN, GE_F32>(d, task, smem, gp, st, phase_id); break;
-    case GL_TN * 8 + GE_STORE: dispatch_bn<GL_TN, GE_STORE>(d, task, smem, gp, st, phase_id); break;
+    case GL_NN * 8 + GE_STORE: dispatch_bn<GL_NN, GE_STORE>(d, task, smem, gp, st, phase_id, et); break;
+    case GL_NN * 8 + GE_RES:   dispatch_bn<GL_NN, GE_RES>(d, task, smem, gp, st, phase_id, et); break;
+    case GL_NN * 8 + GE_GELU:  dispatch_bn<GL_NN, GE_GELU>(d, task, smem, gp, st, phase_id, et); break;
+    case GL_NN * 8 + GE_F32:   dispatch_bn<GL_NN, GE_F32>(d, task, smem, gp, st, phase_id, et); break;      // split-K partial products
+    case GL_NT * 8 + GE_STORE: dispatch_bn<GL_NT, GE_STORE>(d, task, smem, gp, st, phase_id, et); break;
+    case GL_NT * 8 + GE_DGELU: dispatch_bn<GL_NT, GE_DGELU>(d, task, smem, gp, st, phase_id, et); break;
+    case GL_NT * 8 + GE_DR:    gemm_tc_task<GL_NT, GE_DR, 128>(d.g, d.tiles_m, task, smem, gp, st, phase_id, et); break;
+    case GL_NT * 8 + GE_LSE:   gemm_tc_task<GL_NT, GE_LSE, 128>(d.g, d.tiles_m, task, smem, gp, st, phase_id, et); break;
+    case GL_TN * 8 + GE_F32:   dispatch_bn<GL_TN, GE_F32>(d, task, smem, gp, st, phase_id, et); break;
+    case GL_TN * 8 + GE_STORE: dispatch_bn<GL_TN, GE_STORE>(d, task, smem, gp, st, phase_id, et); break;
     default: if (threadIdx.x == 0) raise_abort(st, ST_BAD_DESC, phase_id, task, d.layout * 8 + d.epi); __syncthreads(); break;
   }
 }

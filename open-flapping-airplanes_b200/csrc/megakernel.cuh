@@ -31,7 +31,8 @@ template <class T> struct IsBf16 { static constexpr bool value = std::is_same<T,
 // ---------------------------------------------------------------------------------------------- one training task
 template <class T, int D, int DH>
 __device__ __forceinline__ void run_train_task(const Ctx& C, const PhaseDesc& d, int ph, int local, int step, unsigned char* smem,
-                                               gemm_tc::GemmPipe& gp, attn_tc::AttnPipe& ap, uint32_t& bulk_uses, uint32_t& adam_tiles, uint32_t& ce_chunks) {
+                                               gemm_tc::GemmPipe& gp, attn_tc::AttnPipe& ap, uint32_t& bulk_uses, uint32_t& adam_tiles, uint32_t& ce_chunks,
+                                               const EarlyTicket& et) {
   const ModelDims& md = C.md;
   switch (d.kind) {
     case TK_DATA:
@@ -44,14 +45,14 @@ __device__ __forceinline__ void run_train_task(const Ctx& C, const PhaseDesc& d,
       ew::ln_fwd_task<T, D>(local, (T*)d.p[0], (float*)d.p[1], (float*)d.p[2], (const T*)d.p[3], (const T*)d.p[4], md.N);
       break;
     case TK_GEMM:
-      if constexpr (IsBf16<T>::value) gemm_tc::run(d, local, smem, gp, C.status, ph);
+      if constexpr (IsBf16<T>::value) gemm_tc::run(d, local, smem, gp, C.status, ph, et);
       else f32::gemm_run(d, local, smem);
       break;
     case TK_ATT_FWD: {
       if constexpr (IsBf16<T>::value) {
         const int BH = md.B * md.H, QT = md.T / attn::QTILE;
         const int qt = QT - 1 - local / BH, bh = local % BH;      // heavy (late) query tiles first
-        attn_tc::fwd_task((const attn_tc::Maps*)d.p[6], (bf16*)d.p[1], (float*)d.p[2], bh / md.H, bh % md.H, qt, md.T, md.H, smem, ap, gp.tmem_base, C.status, ph, local);
+        attn_tc::fwd_task((const attn_tc::Maps*)d.p[6], (bf16*)d.p[1], (float*)d.p[2], bh / md.H, bh % md.H, qt, md.T, md.H, smem, ap, gp.tmem_base, C.status, ph, local, et);
       } else {
         f32::attn_fwd_task<DH>((const float*)d.p[0], (float*)d.p[1], (float*)d.p[2], local / md.H, local % md.H, md.T, md.H, smem);
       }
@@ -70,10 +71,10 @@ __device__ __forceinline__ void run_train_task(const Ctx& C, const PhaseDesc& d,
         const int BH = md.B * md.H, QT = md.T / attn::QTILE;
         if (local < BH * QT) {                                     // dK/dV: early key tiles see the most queries -> first
           const int kt = local / BH, bh = local % BH;
-          attn_tc::bwd_dkdv_task((const attn_tc::Maps*)d.p[6], (const float*)d.p[2], (const float*)d.p[3], (bf16*)d.p[4], bh / md.H, bh % md.H, kt, md.T, md.H, smem, ap, gp.tmem_base, C.status, ph, local);
+          attn_tc::bwd_dkdv_task((const attn_tc::Maps*)d.p[6], (const float*)d.p[2], (const float*)d.p[3], (bf16*)d.p[4], bh / md.H, bh % md.H, kt, md.T, md.H, smem, ap, gp.tmem_base, C.status, ph, local, et);
         } else {                                                   // dQ: late query tiles see the most keys -> first
           const int l2 = local - BH * QT, qt = QT - 1 - l2 / BH, bh = l2 % BH;
-          attn_tc::bwd_dq_task((const attn_tc::Maps*)d.p[6], (const float*)d.p[2], (const float*)d.p[3], (bf16*)d.p[4], bh / md.H, bh % md.H, qt, md.T, md.H, smem, ap, gp.tmem_base, C.status, ph, local);
+          attn_tc::bwd_dq_task((const attn_tc::Maps*)d.p[6], (const float*)d.p[2], (const float*)d.p[3], (bf16*)d.p[4], bh / md.H, bh % md.H, qt, md.T, md.H, smem, ap, gp.tmem_base, C.status, ph, local, et);
         }
       } else {
         f32::attn_bwd_task<DH>((const float*)d.p[0], (const float*)d.p[5], (const float*)d.p[1], (const float*)d.p[2], (float*)d.p[4],
@@ -311,6 +312,7 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
   int c_rb_off = -1, c_rb_map = 0;                   // thread 0: where and how the cached phase counts its completions per row block
   int c_ph = -1, c_lo = 0, c_hi = 0, c_mul = 0;      // thread 0: cached phase, its ticket range [c_lo, c_hi) within a step, and its test-only task permutation
   unsigned next_g = 0; bool have_next = false; unsigned claims = 0;   // thread 0: the ticket taken at the end of the previous task
+  const bool early_ok = (C.sched_flags & 4) == 0;   // (flag 4: tickets only at the end of a task, for A/B measurements)
   for (;;) {
     if (tid == 0) {                                  // ---- claim (and, for the training job, wait for the dependencies)
       if (prof) { tl0 = gtimer(); if (tl1) t_tail += tl0 - tl1; }
@@ -414,7 +416,12 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
     if (tid == 0) {
       if (prof) { t0 = gtimer(); t_sync += t0 - tl1; if (job_id == 1 && C.dp.trace && local == 0 && (ph == 0 || ph == 2)) C.dp.trace[16 + ph] = t0; }
     }
-    if (job_id == 0) run_train_task<T, D, DH>(C, d, ph, local, step, smem, gp, ap, bulk_uses, adam_tiles, ce_chunks);
+    if (job_id == 0) {
+      // tensor-core tasks let their copy producer (this block's thread 0) take the next ticket as soon as its last copy is issued
+      const EarlyTicket et = {(use_tc && early_ok) ? J.ticket : nullptr, s_sel + 7};
+      if (tid == 0) s_sel[7] = 0;
+      run_train_task<T, D, DH>(C, d, ph, local, step, smem, gp, ap, bulk_uses, adam_tiles, ce_chunks, et);
+    }
     else run_decode_task<T, D, DH>(C, d, local, smem, fill_bar, fills & 1u);
     if (filled) fills++;
     __syncthreads();
@@ -438,6 +445,7 @@ __device__ void job_loop(const Ctx& C, const Job& J, int job_id, unsigned char* 
     // for the SM's outstanding stores (about a microsecond after a GEMM epilogue); on its own thread it runs beside the ticket's
     // round trip and the next claim instead of in front of them.
     if (tid == 0) {
+      if (job_id == 0 && s_sel[7] != 0) { next_g = (unsigned)s_sel[7] - 1u; have_next = true; }
       if (!have_next) { next_g = atomicAdd(J.ticket, 1u); have_next = true; }
       if (prof) {
         const u64 t1 = gtimer(); tl1 = t1;

@@ -245,7 +245,7 @@ bool upload_job(const std::vector<HostPhase>& ph, int last_phase, int nsteps, De
 // copies a job's scheduling records into the kernel parameter when they fit
 void fill_param_records(Ctx& C, const DevJob* train, const DevJob* dec) {
   C.train_rec_n = 0; C.dec_rec_n = 0;
-  C.sched_flags = 0;
+  C.sched_flags = getenv("OFA_B200_LATE_TICKETS") ? 4 : 0;     // A/B switch for measurements: tickets only at the end of a task
   if (getenv("OFA_B200_GLOBAL_RECS")) return;      // A/B switch for measurements: keep using the records in global memory
   if (train && train->nph > 0 && train->nph <= PARAM_TRAIN_PH) { memcpy(C.train_rec, train->hrec.data(), sizeof(SchedRec) * train->nph); C.train_rec_n = train->nph; }
   if (dec && dec->nph > 0 && dec->nph <= PARAM_DEC_PH) { memcpy(C.dec_rec, dec->hrec.data(), sizeof(SchedRec) * dec->nph); C.dec_rec_n = dec->nph; }
