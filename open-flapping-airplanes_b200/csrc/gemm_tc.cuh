@@ -100,9 +100,11 @@ __device__ __forceinline__ void block_exit(GemmPipe& gp, unsigned char* smem, De
 }
 
 // ---------------------------------------------------------------------------------------------- epilogue math
-// Returns, for GE_DR, the dot product of the eight stored (bf16-rounded) values with the eight aux values; 0 otherwise.
+// The epilogues that meet their second operand in fp32 before the one rounding (and the fp32 result): eight consecutive
+// columns of one row, after the fp32 transpose. Everything else is stored from the bf16-staged pass of the task itself.
 template <int EPI>
-__device__ __forceinline__ float epi_store8(const GemmArgs& g, size_t row, int col, const float* acc, uint4 auxv) {
+__device__ __forceinline__ void epi_store8(const GemmArgs& g, size_t row, int col, const float* acc, uint4 auxv) {
+  static_assert(EPI == GE_F32 || EPI == GE_RES || EPI == GE_DGELU, "bf16 results without a second fp32 operand take the staged pass");
   if constexpr (EPI == GE_F32) {
     float* dst = reinterpret_cast<float*>(g.C) + row * g.ldc + col;
     float4 v0 = make_float4(acc[0], acc[1], acc[2], acc[3]), v1 = make_float4(acc[4], acc[5], acc[6], acc[7]);
@@ -111,38 +113,12 @@ __device__ __forceinline__ float epi_store8(const GemmArgs& g, size_t row, int c
       v0.x += o0.x; v0.y += o0.y; v0.z += o0.z; v0.w += o0.w; v1.x += o1.x; v1.y += o1.y; v1.z += o1.z; v1.w += o1.w;
     }
     *reinterpret_cast<float4*>(dst) = v0; *reinterpret_cast<float4*>(dst + 4) = v1;
-    return 0.f;
   } else {
-    float v[8];
+    float v[8], a8[8];
+    unpack8(auxv, a8);
 #pragma unroll
-    for (int i = 0; i < 8; i++) v[i] = acc[i];
-    bf16* C = reinterpret_cast<bf16*>(g.C);
-    bf16* aux = reinterpret_cast<bf16*>(g.aux);
-    if constexpr (EPI == GE_RES) {
-      float r[8]; unpack8(auxv, r);
-#pragma unroll
-      for (int i = 0; i < 8; i++) v[i] += r[i];
-    } else if constexpr (EPI == GE_GELU) {
-      const uint4 pre = pack8(v);                                   // bf16-rounded pre-activation is what backward sees
-      *reinterpret_cast<uint4*>(aux + row * g.ldaux + col) = pre;
-      float p[8]; unpack8(pre, p);
-#pragma unroll
-      for (int i = 0; i < 8; i++) v[i] = gelu_fwd<true>(p[i]);
-    } else if constexpr (EPI == GE_DGELU) {
-      float p[8]; unpack8(auxv, p);
-#pragma unroll
-      for (int i = 0; i < 8; i++) v[i] *= gelu_bwd<true>(p[i]);
-    }
-    const uint4 out = pack8(v);
-    *reinterpret_cast<uint4*>(C + row * g.ldc + col) = out;
-    if constexpr (EPI == GE_DR) {
-      float c[8], o[8]; unpack8(out, c); unpack8(auxv, o);
-      float s = 0.f;
-#pragma unroll
-      for (int i = 0; i < 8; i++) s = fmaf(c[i], o[i], s);
-      return s;
-    }
-    return 0.f;
+    for (int i = 0; i < 8; i++) v[i] = EPI == GE_RES ? acc[i] + a8[i] : acc[i] * gelu_bwd<true>(a8[i]);
+    *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(g.C) + row * g.ldc + col) = pack8(v);
   }
 }
 
