@@ -126,7 +126,7 @@ __device__ __forceinline__ void epi_store8(const GemmArgs& g, size_t row, int co
 // task index -> (tile_m, first tile_n): consecutive tasks walk down M first so that neighbouring blocks share the B strip.
 template <int LAYOUT, int EPI, int BN>
 __device__ __forceinline__ void gemm_tc_task(const GemmArgs& g, int tiles_m, int task, unsigned char* smem, GemmPipe& gp,
-                                             DevStatus* st, int phase_id, const EarlyTicket& et) {
+                                             DevStatus* st, int phase_id, const EarlyTicket& et, int nfast) {
   using CF = Cfg<BN>;
   constexpr bool A_MN = (LAYOUT == GL_TN), B_MN = (LAYOUT != GL_NT);
   constexpr bool HAS_AUX_IN = (EPI == GE_RES || EPI == GE_DGELU || EPI == GE_DR);
@@ -137,7 +137,10 @@ __device__ __forceinline__ void gemm_tc_task(const GemmArgs& g, int tiles_m, int
   const uint32_t base = smem_u32(smem);
   const int KT = g.K / BK;
   const int tiles_n = g.N / BN;
-  const int tm = task % tiles_m, strip = task / tiles_m;
+  // nfast: consecutive tasks walk along N first, so the tasks that stream the same rows of a large A run side by side and the
+  // second and third reader find them in L2 (the LM head's weight gradient); otherwise down M first, sharing the B strip
+  const int nstrips = (tiles_n + g.nsub - 1) / g.nsub;
+  const int tm = nfast ? task / nstrips : task % tiles_m, strip = nfast ? task % nstrips : task / tiles_m;
   const int tn0 = strip * g.nsub;
   const int nt = min(g.nsub, tiles_n - tn0);
   const int m0 = tm * BM;
@@ -379,8 +382,8 @@ __device__ __forceinline__ void gemm_tc_task(const GemmArgs& g, int tiles_m, int
 
 template <int LAYOUT, int EPI>
 __device__ __forceinline__ void dispatch_bn(const PhaseDesc& d, int task, unsigned char* smem, GemmPipe& gp, DevStatus* st, int phase_id, const EarlyTicket& et) {
-  if (d.g.bn == 256) gemm_tc_task<LAYOUT, EPI, 256>(d.g, d.tiles_m, task, smem, gp, st, phase_id, et);
-  else gemm_tc_task<LAYOUT, EPI, 128>(d.g, d.tiles_m, task, smem, gp, st, phase_id, et);
+  if (d.g.bn == 256) gemm_tc_task<LAYOUT, EPI, 256>(d.g, d.tiles_m, task, smem, gp, st, phase_id, et, d.i0);
+  else gemm_tc_task<LAYOUT, EPI, 128>(d.g, d.tiles_m, task, smem, gp, st, phase_id, et, d.i0);
 }
 // run-time dispatch over the (layout, epilogue) pairs the training graph uses
 __device__ __noinline__ void run(const PhaseDesc& d, int task, unsigned char* smem, GemmPipe& gp, DevStatus* st, int phase_id, const EarlyTicket& et) {
@@ -391,8 +394,8 @@ __device__ __noinline__ void run(const PhaseDesc& d, int task, unsigned char* sm
     case GL_NN * 8 + GE_F32:   dispatch_bn<GL_NN, GE_F32>(d, task, smem, gp, st, phase_id, et); break;      // split-K partial products
     case GL_NT * 8 + GE_STORE: dispatch_bn<GL_NT, GE_STORE>(d, task, smem, gp, st, phase_id, et); break;
     case GL_NT * 8 + GE_DGELU: dispatch_bn<GL_NT, GE_DGELU>(d, task, smem, gp, st, phase_id, et); break;
-    case GL_NT * 8 + GE_DR:    gemm_tc_task<GL_NT, GE_DR, 128>(d.g, d.tiles_m, task, smem, gp, st, phase_id, et); break;
-    case GL_NT * 8 + GE_LSE:   gemm_tc_task<GL_NT, GE_LSE, 128>(d.g, d.tiles_m, task, smem, gp, st, phase_id, et); break;
+    case GL_NT * 8 + GE_DR:    gemm_tc_task<GL_NT, GE_DR, 128>(d.g, d.tiles_m, task, smem, gp, st, phase_id, et, d.i0); break;
+    case GL_NT * 8 + GE_LSE:   gemm_tc_task<GL_NT, GE_LSE, 128>(d.g, d.tiles_m, task, smem, gp, st, phase_id, et, d.i0); break;
     case GL_TN * 8 + GE_F32:   dispatch_bn<GL_TN, GE_F32>(d, task, smem, gp, st, phase_id, et); break;
     case GL_TN * 8 + GE_STORE: dispatch_bn<GL_TN, GE_STORE>(d, task, smem, gp, st, phase_id, et); break;
     default: if (threadIdx.x == 0) raise_abort(st, ST_BAD_DESC, phase_id, task, d.layout * 8 + d.epi); __syncthreads(); break;

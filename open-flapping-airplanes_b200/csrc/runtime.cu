@@ -141,6 +141,9 @@ bool prepare_gemm_bf16(PhaseDesc& d, Arena& ar, int nsub_cfg, int nblocks, std::
   // nsub_cfg: n = strips of n tiles (0 = automatic); 2000 + n = the same with 256-wide tiles where N allows. 256-wide tiles are
   // opt-in: with two 48 KB stages per block they measured slower than three 32 KB stages of the 128-wide tile on every model
   // shape except lm_head dW (960 vs 702 TFLOP/s), i.e. the main loop is bound by bytes in flight, not by operand traffic alone.
+  const bool nfast = nsub_cfg >= 4000;             // 4000 + n: 256-wide tiles and tasks ordered along N first (see gemm_tc_task)
+  if (nfast) nsub_cfg -= 2000;
+  d.i0 = nfast ? 1 : 0;
   const bool want256 = nsub_cfg >= 2000;
   if (want256) nsub_cfg -= 2000;
   g.bn = (want256 && g.N % 256 == 0 && d.epi != GE_DR && d.epi != GE_LSE) ? 256 : 128;
@@ -394,7 +397,9 @@ bool build_train_graph(ofa_ctx* c) {
     PhaseDesc d = mk(TK_GEMM, 0); d.layout = layout; d.epi = epi;
     d.g.A = A; d.g.B = B; d.g.C = Cc; d.g.aux = aux; d.g.M = M; d.g.N = Nn; d.g.K = K; d.g.lda = lda; d.g.ldb = ldb; d.g.ldc = ldc; d.g.ldaux = ldaux;
     d.g.accumulate = accumulate;
-    const int nsub_cfg = (wide && cfg.gemm_nsub == 0 && !getenv("OFA_B200_HEAD_DW_128")) ? 2000 : cfg.gemm_nsub;
+    // wide: 128 x 256 tiles, one tile per task, tasks ordered along N first (the three readers of a 128-row slice of the large
+    // operand run side by side and share it through L2); OFA_B200_HEAD_DW_128 / _STRIPS keep the other two forms for A/B runs
+    const int nsub_cfg = (wide && cfg.gemm_nsub == 0 && !getenv("OFA_B200_HEAD_DW_128")) ? (getenv("OFA_B200_HEAD_DW_STRIPS") ? 2000 : 4001) : cfg.gemm_nsub;
     if (bf) { std::string e; if (!prepare_gemm_bf16(d, c->ar, nsub_cfg, c->C.train_sms > 0 ? 2 * c->C.train_sms : c->nblocks, e)) { ok = false; err = e; } }   // waves are counted over the blocks that train
     else prepare_gemm_f32(d);
     return d;

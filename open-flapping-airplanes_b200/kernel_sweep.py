@@ -51,7 +51,7 @@ def run_gemm(ofa, name, repeats, nsub):
     K = ofa.capi
     layout, epi, Mm, Nn, Kk = GEMMS[name]
     if name == "gemm_head_dW" and nsub == 0:
-        nsub = 2000                      # 128 x 256 tiles, as the training graph runs this one shape (long K, more tiles than blocks)
+        nsub = 4001                      # 128 x 256 tiles, one per task, tasks ordered along N first: as the training graph runs this one shape
     rng = np.random.default_rng(0)
     ashape = (Mm, Kk) if layout != 2 else (Kk, Mm)
     bshape = (Kk, Nn) if layout != 1 else (Nn, Kk)
