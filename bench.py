@@ -37,7 +37,7 @@ FLOP_PER_STEP = 6 * TOKENS_PER_STEP * P_MM + L * 3.5 * (4 * B * H * T * T * (D /
 # dram__bytes_read.sum + dram__bytes_write.sum of the megakernel per step, split workload on one GPU: a constant taken from ONE ncu
 # capture of a 2-step launch (concurrent decoder included), not measured by this program. profiles/ofa_kernel_bench_split_dram_traffic.md
 # holds the command, the raw figures, the date and the commit of the capture; it has to be re-captured when the training graph changes.
-SPLIT_DRAM_BYTES_PER_STEP = 20.3e9
+SPLIT_DRAM_BYTES_PER_STEP = 18.0e9
 
 
 def measured_peaks():
