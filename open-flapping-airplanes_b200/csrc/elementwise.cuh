@@ -381,7 +381,7 @@ __device__ __forceinline__ void ce_task_bulk(int task, bf16* logits, const int* 
 // across row boundaries; nothing waits for a whole row. `bar_lo`, `bar_hi` = two pairs of block-private mbarriers (count 1), `chunks` = running
 // count of chunks this block has staged (advanced identically by every thread). V must be a multiple of 8.
 constexpr int CE_CHUNK = 12288, CE_STAGES = 4;            // elements per chunk (24 KB of bf16)
-__device__ __forceinline__ void ce_task_stream(int task, bf16* logits, const int* targets, float* loss, const float2* part, int tiles_n,
+static __device__ __noinline__ void ce_task_stream(int task, bf16* logits, const int* targets, float* loss, const float2* part, int tiles_n,
                                                int N, int V, float inv_n, unsigned char* smem, uint32_t bar_lo, uint32_t bar_hi, uint32_t& chunks,
                                                const DevStatus* st) {
   auto sbar = [&](uint32_t sg) { return sg < 2 ? bar_lo + 8u * sg : bar_hi + 8u * (sg - 2); };   // the four barriers sit in two free pairs of the control area
@@ -656,7 +656,7 @@ __device__ __forceinline__ void adamw_task(int task, float* W, const GT* G, floa
 // (advanced identically by every thread). The ragged end of a range (fewer than 2,048 elements) goes through the direct loop.
 constexpr int ADAM_TILE = 2048, ADAM_STAGES = 3, ADAM_STAGE_BYTES = 32768;
 template <class T, class GT>
-__device__ __forceinline__ void adamw_task_bulk(int task, float* W, const GT* G, float* M, float* Vv, T* Wact, size_t n, AdamHP hp,
+__device__ __noinline__ void adamw_task_bulk(int task, float* W, const GT* G, float* M, float* Vv, T* Wact, size_t n, AdamHP hp,
                                                 const int2* nodecay, int n_nodecay, unsigned char* smem, uint32_t bar0, uint32_t& tiles,
                                                 const DevStatus* st) {
   const size_t cs = (size_t)task * OPT_CHUNK;
