@@ -493,7 +493,6 @@ bool build_train_graph(ofa_ctx* c) {
     // ---- gradient buckets (only used with ext_sync): head | layer groups from the top | wte+wpe
     std::vector<Bucket> buckets;
     std::vector<int> bucket_of_layer(L, -1);
-  int emb_parts = 1;                                 // pieces the embeddings' bucket is cut into (ext_sync only)
     const bool ext = train && cfg.ext_sync != 0;
     if (ext) {
       const size_t esz = gbf ? 2 : 4, target = cfg.bucket_bytes > 0 ? (size_t)cfg.bucket_bytes : (size_t)25 << 20;
@@ -508,22 +507,8 @@ bool build_train_graph(ofa_ctx* c) {
         buckets.push_back(b);
         hi = lo - 1;
       }
-      {
-        // The embeddings' gradient is the last to be final, so nothing overlaps its all-reduce. Cut into pieces of about the
-        // bucket size (boundaries at AdamW task boundaries), the all-reduce of piece j+1 runs beside the update of piece j.
-        const size_t total = V * D + (size_t)m.T * D;
-        emb_parts = (int)std::min<size_t>(6, std::max<size_t>(1, (total * esz + target / 2) / target));
-        const size_t chunks = (total + ew::OPT_CHUNK - 1) / ew::OPT_CHUNK;
-        size_t c0 = 0;
-        for (int j = 0; j < emb_parts; j++) {
-          const size_t c1 = (j + 1 == emb_parts) ? chunks : chunks * (j + 1) / emb_parts;
-          Bucket b; b.off = lay.wte + c0 * ew::OPT_CHUNK; b.n = std::min(total, c1 * ew::OPT_CHUNK) - c0 * ew::OPT_CHUNK;
-          b.producers = {"embed bwd wte", "embed bwd wpe", "head dX"}; if (lay.tied) b.producers.push_back("head dW");
-          if (emb_parts == 1) b.adam_phases = {"adamw wte", "adamw wpe"}; else b.adam_phases = {"adamw emb ." + std::to_string(j)};
-          b.last_layer = -2; buckets.push_back(b);
-          c0 = c1;
-        }
-      }
+      { Bucket b; b.off = lay.wte; b.n = V * D + (size_t)m.T * D; b.producers = {"embed bwd wte", "embed bwd wpe", "head dX"}; if (lay.tied) b.producers.push_back("head dW");
+        b.adam_phases = {"adamw wte", "adamw wpe"}; b.last_layer = -2; buckets.push_back(b); }
       if (buckets.size() > 32) { c->err = "more than 32 gradient buckets"; return false; }
     }
     c->buckets.clear();
@@ -691,7 +676,7 @@ bool build_train_graph(ofa_ctx* c) {
     { PhaseDesc d = mk(TK_EMB_WTE, (int)((V + ew::EMB_VCHUNK - 1) / ew::EMB_VCHUNK)); d.p[0] = G(lay.wte); d.p[1] = dxs[0]; d.p[2] = c->C.tok_in; d.i0 = lay.tied ? 1 : 0; d.i1 = gbf ? 1 : 0;
       addp("embed bwd wte", d, {"L0 ln1 bwd", lay.tied ? "head dW" : ""}, {}); }
     { PhaseDesc d = mk(TK_EMB_WPE, (m.T + ew::WPE_ROWS - 1) / ew::WPE_ROWS); d.p[0] = G(lay.wpe); d.p[1] = dxs[0]; d.i1 = gbf ? 1 : 0; addp("embed bwd wpe", d, {"L0 ln1 bwd"}, {}); }
-    if (ext) for (int j = emb_parts; j >= 1; j--) signal((int)buckets.size() - j);
+    if (ext) signal((int)buckets.size() - 1);
     end_deps = {"loss mean", "embed bwd wte", "embed bwd wpe", "head dW", "head dX", "lnf dgamma"};
     for (int l = 0; l < L; l++) { const std::string s = "L" + std::to_string(l) + " "; for (const char* nm : {"dWdown", "dWup", "dgamma2", "dWo", "dWqkv", "dgamma1"}) end_deps.push_back(s + nm); }
     if (train) {
@@ -706,20 +691,8 @@ bool build_train_graph(ofa_ctx* c) {
       for (int l = L - 1; l >= 0; l--) if (!id.count("adamw L" + std::to_string(l))) emit_adam_layer(l);
       if (!lay.tied) end_deps.push_back("adamw head");
       for (int l = 0; l < L; l++) end_deps.push_back("adamw L" + std::to_string(l));
-      if (ext && emb_parts > 1) {                        // one update phase per piece of the embeddings' bucket; the two usual names wait for all of them
-        std::vector<std::string> parts;
-        for (int j = 0; j < emb_parts; j++) {
-          const Bucket& b = buckets[buckets.size() - emb_parts + j];
-          const std::string nm = "adamw emb ." + std::to_string(j);
-          addp(nm, mkadam(b.off, b.n, {}), gate(nm, {}), {});
-          parts.push_back(nm);
-        }
-        addp("adamw wte", mk(TK_BARRIER, 1), parts, {});
-        addp("adamw wpe", mk(TK_BARRIER, 1), {"adamw wte"}, {});
-      } else {
-        addp("adamw wte", mkadam(lay.wte, V * D, {}), gate("adamw wte", {"embed bwd wte", "head dX", lay.tied ? "head dW" : ""}), {});
-        addp("adamw wpe", mkadam(lay.wpe, (size_t)m.T * D, {}), gate("adamw wpe", {"embed bwd wpe"}), {});
-      }
+      addp("adamw wte", mkadam(lay.wte, V * D, {}), gate("adamw wte", {"embed bwd wte", "head dX", lay.tied ? "head dW" : ""}), {});
+      addp("adamw wpe", mkadam(lay.wpe, (size_t)m.T * D, {}), gate("adamw wpe", {"embed bwd wpe"}), {});
       end_deps.push_back("adamw wte"); end_deps.push_back("adamw wpe");
     }
   }
