@@ -64,7 +64,7 @@ typedef struct {
   int attn_legacy;          /* must be 0 (the field once selected mma.sync attention tasks kept for comparison; they are gone, the tensor-core tasks are checked against the oracle directly) */
   int adam_interleave;      /* experimental, default 0: 1 = each layer's AdamW phase inside the backward pass; n >= 2 = AdamW trickles through the backward pass, up to n tasks after every backward phase */
   int head_dx_splitk;       /* 1: compute lm_head dX as K-split partial products + reduce (experimental, default 0)     */
-  int gemm_nsub;            /* consecutive 128-wide N tiles per GEMM task (0 = default)                           */
+  int gemm_nsub;            /* consecutive N tiles per GEMM task: n = strips of n 128-wide tiles; 0 = chosen per phase by waves over the blocks that train; 2000 + n = 256-wide tiles where N allows; 4000 + n = the same with a phase's tasks ordered along N first (also accepted as ofa_phase.nsub) */
   double timeout_s;         /* device-side bound for a wait on an external flag (0 = default 20 s); waits for dependencies inside the graph give up after 1.5 x this */
   int device;               /* CUDA device ordinal; < 0 = planning context: layout, buckets and phase graphs are built and can be queried, nothing touches a device and nothing can be launched */
   int sched_profile;        /* 1 (preset default): the kernel keeps the per-phase and per-block time tables that ofa_phase_info / ofa_phase_wait_ns / ofa_phase_window / ofa_read_block_busy / ofa_read_decode_trace report (the reference's report section, ofa.cu:722-746); 0: it does not (they read zero) and every task saves several timer reads and atomics. Step times, losses and live words are kept either way */
